@@ -1,0 +1,355 @@
+"""Seeded synthetic inputs for the beam-search path: vectors, queries, ground truth, graphs.
+
+Stand-ins for the cross-modal datasets the reference is evaluated on (text-to-image
+200-d L2; CLIP-style 512-d inner product, reference README.md:39-45): only their
+shapes, metric and the base/query modality gap are modelled.  Everything here
+produces *inputs* to the search path (a graph, entry points, queries, exact
+ground truth); none of it is on the timed path.  It runs on whatever torch
+device it is given so the same code builds the small CPU test cases and the
+full-size cases on a GPU.
+
+Graph construction follows the shape of the reference's build -- exact k_b-NN
+lists of training queries projected onto the base set, then every node given
+base-space neighbours so none is isolated (reference src/upd_gpu.cu:203-303,
+src/enhance.cu:728-861) -- but is a simplified restatement whose only job is to
+hand the search kernels a CORAL-shaped fixed-degree graph with good recall.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+L2, IP = "l2", "ip"
+
+
+def _gen(seed: int, device) -> torch.Generator:
+    g = torch.Generator(device=device)
+    g.manual_seed(int(seed))
+    return g
+
+
+def _normalize_(x: torch.Tensor) -> torch.Tensor:
+    """Row-wise L2 normalisation as the reference does for inner product
+    (reference src/uni.cpp:38-54): x *= 1/sqrt(sum x^2), rows of norm 0 untouched."""
+    n = x.pow(2).sum(1, keepdim=True).sqrt()
+    inv = torch.where(n > 0, 1.0 / n, torch.ones_like(n))
+    return x.mul_(inv)
+
+
+@dataclass
+class Dataset:
+    base: torch.Tensor          # [N, dim] fp32
+    train: torch.Tensor         # [T, dim] fp32 training queries (used only to build the graph)
+    test: torch.Tensor          # [Q, dim] fp32
+    metric: str
+    name: str
+
+
+def make_l2_mixture(n: int, n_train: int, n_test: int, dim: int = 200, centers: int = 1000,
+                    sigma: float = 0.3, rot_dims: int = 60, offset: float = 0.5,
+                    seed: int = 20260001, device="cpu", chunk: int = 1 << 20) -> Dataset:
+    """Text-to-image-like L2 case: a Gaussian mixture for the base; queries are the same
+    mixture pushed through a fixed random rotation of a `rot_dims` subspace plus a fixed
+    mean offset (the modality gap)."""
+    g = _gen(seed, device)
+    ctr = torch.randn(centers, dim, generator=g, device=device)
+    qr, _ = torch.linalg.qr(torch.randn(rot_dims, rot_dims, generator=g, device=device))
+    off = offset * torch.randn(dim, generator=g, device=device)
+
+    def draw(m, as_query):
+        out = torch.empty(m, dim, device=device)
+        for s in range(0, m, chunk):
+            e = min(m, s + chunk)
+            c = torch.randint(0, centers, (e - s,), generator=g, device=device)
+            x = ctr[c] + sigma * torch.randn(e - s, dim, generator=g, device=device)
+            if as_query:
+                x[:, :rot_dims] = x[:, :rot_dims] @ qr
+                x += off
+            out[s:e] = x
+        return out
+
+    return Dataset(draw(n, False), draw(n_train, True), draw(n_test, True), L2,
+                   f"l2_mixture_{n}x{dim}")
+
+
+def make_ip_cones(n: int, n_train: int, n_test: int, dim: int = 512, clusters: int = 1,
+                  cos_uv: float = 0.3, sigma: float = 0.15, spread: float = 1.0,
+                  seed: int = 20260001, device="cpu", chunk: int = 1 << 20) -> Dataset:
+    """CLIP-like inner-product case: unit vectors.  Base points scatter around a mean
+    direction u, queries around v with cos(u, v) = `cos_uv` (the modality gap).
+    With `clusters` > 1 each base cluster j has its own direction normalise(u + spread*g_j)
+    and a query aimed at cluster j is normalise(v + spread*g_j + noise): the two modalities
+    share the cluster offsets g_j but not the mean direction.  Per-point noise is isotropic
+    with per-coordinate deviation sigma/sqrt(dim) (total deviation `sigma`)."""
+    g = _gen(seed, device)
+    u = torch.randn(dim, generator=g, device=device)
+    u /= u.norm()
+    w = torch.randn(dim, generator=g, device=device)
+    w -= (w @ u) * u
+    w /= w.norm()
+    v = cos_uv * u + math.sqrt(1.0 - cos_uv * cos_uv) * w
+    if clusters > 1:
+        gj = torch.randn(clusters, dim, generator=g, device=device) * (spread / math.sqrt(dim))
+    else:
+        gj = torch.zeros(1, dim, device=device)
+    s = sigma / math.sqrt(dim)
+
+    def draw(m, mean):
+        out = torch.empty(m, dim, device=device)
+        for a in range(0, m, chunk):
+            e = min(m, a + chunk)
+            c = torch.randint(0, gj.shape[0], (e - a,), generator=g, device=device)
+            x = mean + gj[c] + s * torch.randn(e - a, dim, generator=g, device=device)
+            out[a:e] = _normalize_(x)
+        return out
+
+    return Dataset(draw(n, u), draw(n_train, v), draw(n_test, v), IP, f"ip_cones_{n}x{dim}_c{clusters}")
+
+
+# ----------------------------------------------------------------------------------------------
+# exact k-NN (ground truth and training lists)
+# ----------------------------------------------------------------------------------------------
+
+def _scores(q: torch.Tensor, b: torch.Tensor, metric: str, b_sq=None) -> torch.Tensor:
+    """Larger = closer.  fp32 matmul (TF32 is switched off by the callers)."""
+    s = q @ b.T
+    if metric == L2:
+        if b_sq is None:
+            b_sq = b.pow(2).sum(1)
+        s = 2.0 * s - b_sq[None, :]          # -(|b|^2 - 2 q.b): |q|^2 is constant per row
+    return s
+
+
+@torch.no_grad()
+def exact_knn(base: torch.Tensor, queries: torch.Tensor, k: int, metric: str,
+              q_chunk: int = 2048, b_chunk: int = 262144) -> torch.Tensor:
+    """Exact k nearest base rows per query (ties broken by the smaller id), int32 [Q, k]."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        n = base.shape[0]
+        out = torch.empty(queries.shape[0], k, dtype=torch.int32, device=base.device)
+        for qs in range(0, queries.shape[0], q_chunk):
+            q = queries[qs:qs + q_chunk]
+            best_s = best_i = None
+            for bs in range(0, n, b_chunk):
+                b = base[bs:bs + b_chunk]
+                s = _scores(q, b, metric)
+                kk = min(k, s.shape[1])
+                ts, ti = torch.topk(s, kk, dim=1)
+                ti = ti + bs
+                if best_s is None:
+                    best_s, best_i = ts, ti
+                else:
+                    cs = torch.cat([best_s, ts], 1)
+                    ci = torch.cat([best_i, ti], 1)
+                    o = torch.topk(cs, min(k, cs.shape[1]), dim=1).indices
+                    best_s, best_i = cs.gather(1, o), ci.gather(1, o)
+            # order by (score desc, id asc)
+            key = torch.argsort(best_i, dim=1, stable=True)
+            bs_, bi_ = best_s.gather(1, key), best_i.gather(1, key)
+            key = torch.argsort(bs_, dim=1, descending=True, stable=True)
+            out[qs:qs + q.shape[0]] = bi_.gather(1, key)[:, :k].to(torch.int32)
+        return out
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+# ----------------------------------------------------------------------------------------------
+# graph construction
+# ----------------------------------------------------------------------------------------------
+
+@dataclass
+class Graph:
+    adj: torch.Tensor        # int32 [N, deg_pad], -1 padded, valid ids first
+    start_ids: torch.Tensor  # int32 [M]
+    max_degree: int
+
+
+def _pad_degree(max_degree: int) -> int:
+    return 32 * ((max_degree + 31) // 32)
+
+
+@torch.no_grad()
+def _coarse_assign(base: torch.Tensor, n_cells: int, metric: str, seed: int, iters: int = 2,
+                   chunk: int = 1 << 18):
+    """A few Lloyd iterations from sampled centroids; returns cell id per base row."""
+    n = base.shape[0]
+    g = _gen(seed, base.device)
+    cent = base[torch.randperm(n, generator=g, device=base.device)[:n_cells]].clone()
+    assign = torch.empty(n, dtype=torch.int64, device=base.device)
+    for it in range(iters + 1):
+        c_sq = cent.pow(2).sum(1)
+        for s in range(0, n, chunk):
+            assign[s:s + chunk] = _scores(base[s:s + chunk], cent, L2, c_sq).argmax(1)
+        if it == iters:
+            break
+        sums = torch.zeros_like(cent).index_add_(0, assign, base)
+        cnt = torch.bincount(assign, minlength=n_cells).clamp_(min=1).to(base.dtype)
+        cent = sums / cnt[:, None]
+    return assign
+
+
+@torch.no_grad()
+def _cell_knn(base: torch.Tensor, assign: torch.Tensor, n_cells: int, kk: int, metric: str):
+    """Base-space k-NN restricted to each node's coarse cell.  int32 [N, kk], -1 padded."""
+    n = base.shape[0]
+    order = torch.argsort(assign, stable=True)
+    counts = torch.bincount(assign, minlength=n_cells).tolist()
+    out = torch.full((n, kk), -1, dtype=torch.int32, device=base.device)
+    pos = 0
+    for c in range(n_cells):
+        m = counts[c]
+        if m == 0:
+            continue
+        ids = order[pos:pos + m]
+        pos += m
+        if m == 1:
+            continue
+        x = base[ids]
+        for s in range(0, m, 8192):
+            xs = x[s:s + 8192]
+            sc = _scores(xs, x, metric)
+            if metric == L2:
+                pass
+            r = torch.arange(s, s + xs.shape[0], device=base.device)
+            sc[torch.arange(xs.shape[0], device=base.device), r] = -float("inf")
+            t = min(kk, m - 1)
+            nb = torch.topk(sc, t, dim=1).indices
+            out[ids[s:s + xs.shape[0]], :t] = ids[nb].to(torch.int32)
+    return out
+
+
+@torch.no_grad()
+def build_graph(base: torch.Tensor, train: torch.Tensor, metric: str, max_degree: int = 32,
+                k_b: int = 100, n_start: int = 16, seed: int = 20260004,
+                train_knn: torch.Tensor | None = None, nap_per_node: int = 12,
+                cell_size: int = 2048, list_batch: int = 2048, routers: bool = True) -> Graph:
+    """Fixed-degree directed graph in the reference's spirit.
+
+    1. k_b-NN list of every training query (exact unless `train_knn` is given).
+    2. Projection: inside each list, every member proposes its `nap_per_node`
+       closest co-members (base-space distance) as out-neighbours and is proposed
+       as in-neighbour in return.
+    3. Every node also proposes its base-space neighbours inside its coarse cell,
+       so nodes no training query reached still get in- and out-edges.
+    4. Per node: proposals deduplicated, projection edges first then cell edges,
+       each group closest first, cut to `max_degree`.
+    5. Entry points: the closest base point to each of `n_start` k-means centroids
+       of the training queries; with `routers`, each entry point's row is replaced by
+       "router" nodes (closest base points to a finer k-means of the training queries).
+    """
+    dev = base.device
+    n, dim = base.shape
+    deg_pad = _pad_degree(max_degree)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        if train_knn is None:
+            train_knn = exact_knn(base, train, min(k_b, n), metric)
+        kb = train_knn.shape[1]
+        m = min(nap_per_node, kb - 1)
+
+        src_l, dst_l, d_l = [], [], []
+        for s in range(0, train_knn.shape[0], list_batch):
+            ids = train_knn[s:s + list_batch].long()              # [B, kb]
+            x = base[ids]                                         # [B, kb, dim]
+            sc = torch.bmm(x, x.transpose(1, 2))                  # [B, kb, kb]
+            if metric == L2:
+                sq = x.pow(2).sum(2)
+                sc = 2.0 * sc - sq[:, None, :] - sq[:, :, None]    # -|a-b|^2
+            eye = torch.eye(kb, dtype=torch.bool, device=dev)[None]
+            sc = sc.masked_fill(eye, -float("inf"))
+            ts, ti = torch.topk(sc, m, dim=2)                     # [B, kb, m]
+            u = ids[:, :, None].expand(-1, -1, m)
+            v = ids.gather(1, ti.reshape(ids.shape[0], -1)).reshape(ids.shape[0], kb, m)
+            src_l += [u.reshape(-1), v.reshape(-1)]               # forward and reverse proposals
+            dst_l += [v.reshape(-1), u.reshape(-1)]
+            d_l += [-ts.reshape(-1), -ts.reshape(-1)]
+        src = torch.cat(src_l)
+        dst = torch.cat(dst_l)
+        dd = torch.cat(d_l)
+        del src_l, dst_l, d_l
+
+        n_cells = max(1, n // cell_size)
+        assign = _coarse_assign(base, n_cells, metric, seed)
+        cell_nb = _cell_knn(base, assign, n_cells, max_degree, metric)  # [N, R]
+        cu = torch.arange(n, device=dev)[:, None].expand(-1, cell_nb.shape[1]).reshape(-1)
+        cv = cell_nb.reshape(-1).long()
+        keep = cv >= 0
+        cu, cv = cu[keep], cv[keep]
+        # rank inside the cell list is already closest first: use it as the distance key
+        cr = torch.arange(cell_nb.shape[1], device=dev, dtype=torch.float32)[None, :].expand(n, -1).reshape(-1)[keep]
+
+        # group key: (node, class, distance); class 0 = projection edge, 1 = cell edge
+        all_u = torch.cat([src, cu])
+        all_v = torch.cat([dst, cv])
+        all_c = torch.cat([torch.zeros_like(src), torch.ones_like(cu)])
+        all_d = torch.cat([dd, cr])
+        del src, dst, dd, cu, cv, cr
+        # dedupe (u, v): keep the first occurrence in (u, v, class) order
+        o = torch.argsort(all_c, stable=True)
+        all_u, all_v, all_c, all_d = all_u[o], all_v[o], all_c[o], all_d[o]
+        o = torch.argsort(all_u * n + all_v, stable=True)
+        all_u, all_v, all_c, all_d = all_u[o], all_v[o], all_c[o], all_d[o]
+        first = torch.ones_like(all_u, dtype=torch.bool)
+        first[1:] = (all_u[1:] != all_u[:-1]) | (all_v[1:] != all_v[:-1])
+        all_u, all_v, all_c, all_d = all_u[first], all_v[first], all_c[first], all_d[first]
+        # order inside a node: class, then distance
+        o = torch.argsort(all_d, stable=True)
+        all_u, all_v, all_c = all_u[o], all_v[o], all_c[o]
+        o = torch.argsort(all_u * 2 + all_c, stable=True)
+        all_u, all_v = all_u[o], all_v[o]
+        start = torch.zeros(n + 1, dtype=torch.int64, device=dev)
+        start[1:] = torch.cumsum(torch.bincount(all_u, minlength=n), 0)
+        rank = torch.arange(all_u.shape[0], device=dev) - start[all_u]
+        keep = rank < max_degree
+        adj = torch.full((n, deg_pad), -1, dtype=torch.int32, device=dev)
+        adj[all_u[keep], rank[keep]] = all_v[keep].to(torch.int32)
+
+        # entry points and routers: k-means of the training queries; the base point closest
+        # to each of `n_start` coarse centroids is an entry point, and the row of entry point
+        # i is replaced by the base points closest to the i-th slice of n_start*max_degree
+        # fine centroids, so that one expansion round fans out over the whole query space.
+        def kmeans_nearest(kc, sd):
+            g = _gen(sd, dev)
+            kc = min(kc, train.shape[0])
+            cent = train[torch.randperm(train.shape[0], generator=g, device=dev)[:kc]].clone()
+            for _ in range(4):
+                a = _scores(train, cent, L2).argmax(1)
+                sums = torch.zeros_like(cent).index_add_(0, a, train)
+                cnt = torch.bincount(a, minlength=cent.shape[0]).clamp_(min=1).to(train.dtype)
+                cent = sums / cnt[:, None]
+            if metric == IP:
+                cent = _normalize_(cent)
+            return exact_knn(base, cent, 1, metric)[:, 0].long()
+
+        start_ids = torch.unique(kmeans_nearest(4 * n_start, seed + 1))[:n_start]
+        if routers and n > 4 * n_start * max_degree:
+            rt = torch.unique(kmeans_nearest(n_start * max_degree, seed + 2))
+            rt = rt[~torch.isin(rt, start_ids)]
+            rows = torch.full((start_ids.shape[0] * max_degree,), -1, dtype=torch.int32, device=dev)
+            rows[:rt.shape[0]] = rt.to(torch.int32)[:rows.shape[0]]
+            rows = rows.reshape(start_ids.shape[0], max_degree).T.contiguous().T  # keep row-major
+            # valid ids first inside every row
+            o = torch.argsort((rows < 0).to(torch.int8), dim=1, stable=True)
+            adj[start_ids, :max_degree] = rows.gather(1, o)
+            adj[start_ids, max_degree:] = -1
+        return Graph(adj.contiguous(), start_ids.to(torch.int32), max_degree)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+def random_graph(n: int, max_degree: int, n_start: int = 16, seed: int = 7, min_degree: int = 0,
+                 device="cpu") -> Graph:
+    """Uniform random neighbours with ragged degrees (for tests that need no recall)."""
+    g = _gen(seed, device)
+    deg_pad = _pad_degree(max_degree)
+    adj = torch.randint(0, n, (n, deg_pad), generator=g, device=device, dtype=torch.int32)
+    deg = torch.randint(min_degree, max_degree + 1, (n,), generator=g, device=device)
+    col = torch.arange(deg_pad, device=device)[None, :]
+    adj = torch.where(col < deg[:, None], adj, torch.full_like(adj, -1))
+    start = torch.randperm(n, generator=g, device=device)[:n_start].to(torch.int32)
+    return Graph(adj.contiguous(), start, max_degree)

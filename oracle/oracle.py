@@ -1,0 +1,193 @@
+"""ctypes access to the CPU checkers (test infrastructure, not product code).
+
+Only tests, the smoke check and the benchmark's baseline legs may import this
+module.  ``liboracle.so`` holds the restatement of the reference GPU kernel's
+semantics (``beam_search_oracle.c``) and the self-contained CPU best-first port
+(``search_in_cpu_port.c``); ``_ref/libref_cpu.so`` is the same best-first loop
+driving the reference's own queue and AVX-512 distance classes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+L2, IP = 0, 1
+STATS_W = 8
+STAT_NAMES = ("status", "n_dist", "n_exp", "rounds", "hops", "n_scan", "max_cand", "n_visited")
+
+_lib = None
+_ref = None
+
+
+def build(quiet: bool = True) -> None:
+    """Compile the checkers (and ``_ref`` when the reference tree is present)."""
+    subprocess.run(["make", "-C", _HERE], check=True,
+                   stdout=subprocess.DEVNULL if quiet else None)
+
+
+def _load():
+    global _lib
+    if _lib is None:
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path):
+            build()
+        _lib = C.CDLL(path)
+        f32p, i32p = C.POINTER(C.c_float), C.POINTER(C.c_int32)
+        _lib.coral_oracle_search.restype = C.c_int
+        _lib.coral_oracle_search.argtypes = [
+            f32p, C.c_int64, C.c_int, i32p, C.c_int, i32p, C.c_int, f32p, C.c_int, C.c_int, C.c_int,
+            C.c_int, C.c_int, i32p, f32p, i32p, C.c_int]
+        _lib.coral_oracle_dist_seq.restype = C.c_float
+        _lib.coral_oracle_dist_seq.argtypes = [f32p, f32p, C.c_int, C.c_int]
+        _lib.coral_oracle_dist_tree.restype = C.c_float
+        _lib.coral_oracle_dist_tree.argtypes = [f32p, f32p, C.c_int, C.c_int]
+        _lib.coral_oracle_merge_shards.restype = C.c_int
+        _lib.coral_oracle_merge_shards.argtypes = [i32p, f32p, C.c_int, C.c_int, C.c_int, C.c_int, i32p, f32p]
+        _lib.coral_oracle_recall.restype = C.c_double
+        _lib.coral_oracle_recall.argtypes = [i32p, i32p, C.c_int, C.c_int, C.c_int]
+        _set_cpu_sig(_lib)
+    return _lib
+
+
+def _set_cpu_sig(lib):
+    f32p, i32p = C.POINTER(C.c_float), C.POINTER(C.c_int32)
+    lib.coral_cpu_search.restype = C.c_int
+    lib.coral_cpu_search.argtypes = [
+        f32p, C.c_int64, C.c_int, i32p, C.c_int, i32p, C.c_int, f32p, C.c_int, C.c_int, C.c_int,
+        i32p, f32p, C.POINTER(C.c_int64), C.POINTER(C.c_double), C.c_int]
+    lib.coral_cpu_search_kind.restype = C.c_int
+
+
+def _f32(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return a, a.ctypes.data_as(C.POINTER(C.c_float))
+
+
+def _i32(a):
+    a = np.ascontiguousarray(a, dtype=np.int32)
+    return a, a.ctypes.data_as(C.POINTER(C.c_int32))
+
+
+def metric_id(metric) -> int:
+    if metric in (L2, "l2", "L2"):
+        return L2
+    if metric in (IP, "ip", "IP"):
+        return IP
+    raise ValueError(f"unknown metric {metric!r}")
+
+
+def search(base, adj, start_ids, queries, L, k, metric, order=0, threads=0):
+    """Full-expansion beam search as the reference GPU kernel defines it.
+
+    Returns (ids[Q,k] int32, dists[Q,k] float32, stats[Q,8] int32).
+    """
+    lib = _load()
+    base, bp = _f32(base)
+    adj, ap = _i32(adj)
+    start_ids, sp = _i32(start_ids)
+    queries, qp = _f32(queries)
+    n, dim = base.shape
+    Q = queries.shape[0]
+    ids = np.empty((Q, k), np.int32)
+    dists = np.empty((Q, k), np.float32)
+    stats = np.zeros((Q, STATS_W), np.int32)
+    rc = lib.coral_oracle_search(bp, n, dim, ap, adj.shape[1], sp, len(start_ids), qp, Q, L, k,
+                                 metric_id(metric), order,
+                                 ids.ctypes.data_as(C.POINTER(C.c_int32)),
+                                 dists.ctypes.data_as(C.POINTER(C.c_float)),
+                                 stats.ctypes.data_as(C.POINTER(C.c_int32)), threads)
+    if rc != 0:
+        raise ValueError("coral_oracle_search: bad arguments")
+    return ids, dists, stats
+
+
+def dist_seq(row, q, metric):
+    lib = _load()
+    row, rp = _f32(row)
+    q, qp = _f32(q)
+    return np.float32(lib.coral_oracle_dist_seq(rp, qp, row.size, metric_id(metric)))
+
+
+def dist_tree(row, q, metric):
+    lib = _load()
+    row, rp = _f32(row)
+    q, qp = _f32(q)
+    return np.float32(lib.coral_oracle_dist_tree(rp, qp, row.size, metric_id(metric)))
+
+
+def merge_shards(ids, dists, metric):
+    """ids/dists: [G,Q,k] -> merged ([Q,k], [Q,k]) by (distance, id)."""
+    lib = _load()
+    ids, ip_ = _i32(ids)
+    dists, dp = _f32(dists)
+    G, Q, k = ids.shape
+    oi = np.empty((Q, k), np.int32)
+    od = np.empty((Q, k), np.float32)
+    rc = lib.coral_oracle_merge_shards(ip_, dp, G, Q, k, metric_id(metric),
+                                       oi.ctypes.data_as(C.POINTER(C.c_int32)),
+                                       od.ctypes.data_as(C.POINTER(C.c_float)))
+    if rc != 0:
+        raise ValueError("coral_oracle_merge_shards: bad arguments")
+    return oi, od
+
+
+def recall(res, gt, k):
+    lib = _load()
+    res, rp = _i32(res)
+    gt, gp = _i32(gt)
+    return float(lib.coral_oracle_recall(rp, gp, res.shape[0], k, gt.shape[1]))
+
+
+def _cpu_has(flag: str) -> bool:
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("flags"):
+                    return flag in line.split()
+    except OSError:
+        pass
+    return False
+
+
+def cpu_search_lib(prefer_reference: bool = True):
+    """Return (lib, kind): kind 'reference' when the harness on the reference's own
+    headers is built and this CPU has the AVX-512 it needs, else 'port'."""
+    global _ref
+    path = os.path.join(_HERE, "_ref", "libref_cpu.so")
+    if prefer_reference and os.path.exists(path) and _cpu_has("avx512f") and _cpu_has("avx512dq"):
+        if _ref is None:
+            _ref = C.CDLL(path)
+            _set_cpu_sig(_ref)
+        return _ref, "reference"
+    return _load(), "port"
+
+
+def cpu_search(base, adj, start_ids, queries, L, k, threads=0, prefer_reference=True):
+    """The reference's CPU best-first search (always squared L2, first M start ids).
+
+    Returns (ids, dists, total_hops, seconds, kind, threads_used).
+    """
+    lib, kind = cpu_search_lib(prefer_reference)
+    base, bp = _f32(base)
+    adj, ap = _i32(adj)
+    start_ids, sp = _i32(start_ids)
+    queries, qp = _f32(queries)
+    n, dim = base.shape
+    Q = queries.shape[0]
+    ids = np.empty((Q, k), np.int32)
+    dists = np.empty((Q, k), np.float32)
+    hops = C.c_int64(0)
+    secs = C.c_double(0.0)
+    if threads <= 0:
+        threads = os.cpu_count() or 1
+    rc = lib.coral_cpu_search(bp, n, dim, ap, adj.shape[1], sp, len(start_ids), qp, Q, L, k,
+                              ids.ctypes.data_as(C.POINTER(C.c_int32)),
+                              dists.ctypes.data_as(C.POINTER(C.c_float)),
+                              C.byref(hops), C.byref(secs), threads)
+    if rc != 0:
+        raise ValueError("coral_cpu_search: bad arguments")
+    return ids, dists, int(hops.value), float(secs.value), kind, threads
