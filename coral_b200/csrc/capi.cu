@@ -1,0 +1,726 @@
+// C ABI of the beam-search path: handle management, shared-memory planning,
+// host<->device staging, the small companion kernels (hit count, shard merge,
+// id mapping).  There is no CPU fallback: without a CUDA device every entry
+// point that needs one returns CORAL_ERR_NOGPU.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/coral_b200.h"
+#include "search_kernel.cuh"
+
+using coral::SearchArgs;
+using coral::SearchPlan;
+
+namespace {
+
+thread_local std::string g_create_error;
+
+struct Options {
+    int ctas_per_sm = 2;
+    int warps = 4;
+    int chunk_bytes = 256;
+    int stages = 0;  // 0 = as many as fit (at most 6)
+    int smem_hash_bits = 12;
+    int ghash_factor = 8;  // global visited table entries >= factor * L * deg_pad
+    int ghash_entries = 0; // explicit table size (power of two >= 64), 0 = from ghash_factor
+    int max_rounds = 1 << 16;
+};
+
+}  // namespace
+
+struct coral_index {
+    int device = 0;
+    int sm_count = 0;
+    int smem_optin = 0;
+    int64_t n = 0;
+    int dim = 0, max_degree = 0, deg_pad = 0, metric = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev_t0 = nullptr, ev_k0 = nullptr, ev_k1 = nullptr, ev_t1 = nullptr;
+
+    float* d_vecs = nullptr;
+    bool own_vecs = false;
+    int32_t* d_adj = nullptr;
+    int32_t* d_start = nullptr;
+    int M = 0;
+    uint32_t* d_deleted = nullptr;
+
+    Options opt;
+    bool prepared = false;
+    int max_q = 0, max_L = 0, max_k = 0;
+    int grid_cap = 0;
+    uint32_t gh_entries = 0;
+    uint32_t epoch_base = 0;
+    uint64_t* d_ghash = nullptr;
+    uint64_t* d_gcand = nullptr;
+    size_t cand_cap_alloc = 0;
+    float* d_queries = nullptr;
+    int32_t* d_ids = nullptr;
+    float* d_dists = nullptr;
+    int32_t* d_stats = nullptr;
+    unsigned long long* d_ctrl = nullptr;  // [0] q_counter(int) | err(int), [1] hops_total
+    unsigned long long* h_ctrl = nullptr;  // pinned mirror
+    int64_t* d_hits = nullptr;
+    std::map<int, std::pair<SearchPlan, int>> plans;  // L -> (plan, CTAs per SM)
+
+    float last_kernel_ms = 0.f, last_total_ms = 0.f;
+    int64_t launches = 0;
+    std::string err;
+};
+
+namespace {
+
+int fail(coral_index* h, int code, const std::string& msg) {
+    if (h)
+        h->err = msg;
+    else
+        g_create_error = msg;
+    return code;
+}
+
+#define CK(call)                                                                                  \
+    do {                                                                                          \
+        cudaError_t e_ = (call);                                                                  \
+        if (e_ != cudaSuccess) {                                                                  \
+            cudaGetLastError();                                                                   \
+            return fail(h, CORAL_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e_));   \
+        }                                                                                         \
+    } while (0)
+
+bool is_device_ptr(const void* p) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+}
+
+int next_pow2(int x) {
+    int p = 1;
+    while (p < x) p <<= 1;
+    return p;
+}
+
+int align_up(int x, int a) { return (x + a - 1) / a * a; }
+
+// Shared-memory plan for beam capacity L; returns false when nothing fits.
+bool make_plan(const coral_index* h, int L, SearchPlan& p, std::string& why) {
+    const Options& o = h->opt;
+    const int row_bytes = h->dim * 4;
+    p = SearchPlan{};
+    p.warps = std::min(std::max(o.warps, 1), 16);
+    p.ctas_per_sm = std::min(std::max(o.ctas_per_sm, 1), 8);
+    int target = std::max(16, o.chunk_bytes);
+    int nc = (row_bytes + target - 1) / target;
+    while (nc <= row_bytes / 16 && !(row_bytes % nc == 0 && (row_bytes / nc) % 16 == 0)) ++nc;
+    if (nc > row_bytes / 16) {
+        why = "row size has no 16-byte chunking";
+        return false;
+    }
+    p.n_chunks = nc;
+    p.chunk_bytes = row_bytes / nc;
+    p.row_stride = p.chunk_bytes + (((p.chunk_bytes / 16) % 2 == 0) ? 16 : 0);
+    p.stage_bytes = 32 * p.row_stride;
+    p.LP = next_pow2(std::max(L, 32));
+    p.hs_bits = std::min(std::max(o.smem_hash_bits, 0), 16);
+
+    const int budget = h->smem_optin / p.ctas_per_sm - 1024;  // the runtime keeps 1 KB per CTA
+    for (;;) {
+        int off = 0;
+        p.off_query = off;  off = align_up(off + h->dim * 4, 16);
+        p.off_beam0 = off;  off += p.LP * 8;
+        p.off_beam1 = off;  off += p.LP * 8;
+        p.off_exp = off;    off = align_up(off + L * 4, 16);
+        p.off_hash = off;   off += p.hs_bits > 0 ? (4 << p.hs_bits) : 0;
+        p.off_bar = off;    off += p.warps * 8 * 8;  // room for up to 8 stages
+        p.off_pend = off;   off += p.warps * 160 * 4;
+        p.off_bids = off;   off += p.warps * 64 * 4;
+        off = align_up(off, 128);
+        p.off_stage = off;
+        const int room = budget - off;
+        int st = room / (p.warps * p.stage_bytes);
+        if (o.stages > 0) st = std::min(st, o.stages);
+        st = std::min(st, 6);
+        if (st >= 1 && (st >= 2 || p.hs_bits == 0)) {
+            p.stages = st;
+            p.smem_bytes = off + p.warps * st * p.stage_bytes;
+            break;
+        }
+        if (p.hs_bits > 0) {  // shrink the shared hash before giving up
+            p.hs_bits = p.hs_bits > 8 ? p.hs_bits - 1 : 0;
+            continue;
+        }
+        if (st >= 1) {
+            p.stages = st;
+            p.smem_bytes = off + p.warps * st * p.stage_bytes;
+            break;
+        }
+        why = "shared memory budget too small for this dim/L/warps/ctas_per_sm";
+        return false;
+    }
+    int tile = 64;
+    const int cap = std::min(p.warps * p.stages * p.stage_bytes / 8, 2048);
+    while (tile * 2 <= cap) tile <<= 1;
+    p.tile_max = tile;
+    if (p.tile_max < p.warps * 32) {
+        why = "staging area too small to sort a candidate tile";
+        return false;
+    }
+    return true;
+}
+
+int get_plan(coral_index* h, int L, SearchPlan& p, int& per_sm) {
+    auto it = h->plans.find(L);
+    if (it != h->plans.end()) {
+        p = it->second.first;
+        per_sm = it->second.second;
+        return CORAL_OK;
+    }
+    std::string why;
+    if (!make_plan(h, L, p, why)) return fail(h, CORAL_ERR_ARG, why);
+    per_sm = coral::beam_search_occupancy(p, h->metric);
+    if (per_sm <= 0) return fail(h, CORAL_ERR_CUDA, "kernel does not fit an SM with this plan");
+    per_sm = std::min(per_sm, p.ctas_per_sm);
+    h->plans[L] = {p, per_sm};
+    return CORAL_OK;
+}
+
+// ------------------------------------------------------------------ companion kernels
+
+__global__ void count_hits_kernel(const int32_t* __restrict__ res, const int32_t* __restrict__ gt, int Q, int k,
+                                  int gt_dim, unsigned long long* hits) {
+    unsigned long long local = 0;
+    const long long total = (long long)Q * k;
+    for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total;
+         t += (long long)gridDim.x * blockDim.x) {
+        const int q = (int)(t / k), j = (int)(t % k);
+        const int p = gt[(size_t)q * gt_dim + j];
+        const int32_t* r = res + (size_t)q * k;
+        for (int i = 0; i < k; ++i)
+            if (r[i] == p) {
+                ++local;
+                break;
+            }
+    }
+    for (int off = 16; off > 0; off >>= 1) local += __shfl_down_sync(0xffffffffu, local, off);
+    if ((threadIdx.x & 31) == 0 && local) atomicAdd(hits, local);
+}
+
+__device__ __forceinline__ uint32_t ord32(float d, int metric) {
+    if (metric == 1) d = -d;
+    uint32_t u = __float_as_uint(d);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float unord32(uint32_t o, int metric) {
+    uint32_t u = (o & 0x80000000u) ? (o & 0x7fffffffu) : ~o;
+    float d = __uint_as_float(u);
+    return metric == 1 ? -d : d;
+}
+
+// One warp per query: the G*k per-shard results are sorted by (distance, id) in
+// shared memory and the first k written out.
+__global__ void merge_shards_kernel(const int32_t* __restrict__ ids, const float* __restrict__ dists, int G,
+                                    int Q, int k, int n2, int metric, int32_t* __restrict__ ids_out,
+                                    float* __restrict__ dists_out) {
+    extern __shared__ unsigned long long msm[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+    unsigned long long* s = msm + (size_t)warp * n2;
+    for (int q = blockIdx.x * wpb + warp; q < Q; q += gridDim.x * wpb) {
+        for (int i = lane; i < n2; i += 32) {
+            unsigned long long key = ~0ull;
+            if (i < G * k) {
+                const int g = i / k, j = i - g * k;
+                const size_t o = ((size_t)g * Q + q) * k + j;
+                const int id = ids[o];
+                if (id >= 0) key = ((unsigned long long)ord32(dists[o], metric) << 32) | (uint32_t)id;
+            }
+            s[i] = key;
+        }
+        __syncwarp();
+        for (int kk = 2; kk <= n2; kk <<= 1)
+            for (int j = kk >> 1; j > 0; j >>= 1) {
+                for (int i = lane; i < n2; i += 32) {
+                    const int ixj = i ^ j;
+                    if (ixj > i) {
+                        const unsigned long long a = s[i], b = s[ixj];
+                        if ((a > b) == ((i & kk) == 0)) {
+                            s[i] = b;
+                            s[ixj] = a;
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+        for (int i = lane; i < k; i += 32) {
+            const unsigned long long key = s[i];
+            if (key == ~0ull) {
+                ids_out[(size_t)q * k + i] = -1;
+                dists_out[(size_t)q * k + i] = metric == 0 ? 3.402823466e+38f : -3.402823466e+38f;
+            } else {
+                ids_out[(size_t)q * k + i] = (int32_t)(uint32_t)key;
+                dists_out[(size_t)q * k + i] = unord32((uint32_t)(key >> 32), metric);
+            }
+        }
+        __syncwarp();
+    }
+}
+
+__global__ void map_ids_kernel(int32_t* ids, long long count, const int32_t* __restrict__ id_map) {
+    for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < count;
+         t += (long long)gridDim.x * blockDim.x) {
+        const int v = ids[t];
+        if (v >= 0) ids[t] = id_map[v];
+    }
+}
+
+int ensure_device(coral_index* h) {
+    CK(cudaSetDevice(h->device));
+    return CORAL_OK;
+}
+
+void free_search(coral_index* h) {
+    cudaFree(h->d_ghash);   h->d_ghash = nullptr;
+    cudaFree(h->d_gcand);   h->d_gcand = nullptr;
+    cudaFree(h->d_queries); h->d_queries = nullptr;
+    cudaFree(h->d_ids);     h->d_ids = nullptr;
+    cudaFree(h->d_dists);   h->d_dists = nullptr;
+    cudaFree(h->d_stats);   h->d_stats = nullptr;
+    h->prepared = false;
+    h->plans.clear();
+}
+
+}  // namespace
+
+extern "C" {
+
+int coral_version(void) { return 100; }
+int coral_compiled_sm(void) { return 100; }
+
+const char* coral_last_error(coral_index_t* h) { return h ? h->err.c_str() : g_create_error.c_str(); }
+
+int coral_index_create(coral_index_t** out, int device, int64_t n, int dim, int max_degree, int metric) {
+    coral_index* h = nullptr;
+    if (!out) return fail(h, CORAL_ERR_ARG, "out is null");
+    *out = nullptr;
+    if (n <= 0 || n > 0x7fffffffll) return fail(h, CORAL_ERR_ARG, "n must be in [1, 2^31)");
+    if (dim <= 0 || dim % 4 != 0) return fail(h, CORAL_ERR_ARG, "dim must be a positive multiple of 4");
+    if (max_degree <= 0 || max_degree > 128) return fail(h, CORAL_ERR_ARG, "max_degree must be in [1, 128]");
+    if (metric != CORAL_L2 && metric != CORAL_IP) return fail(h, CORAL_ERR_ARG, "metric must be CORAL_L2 or CORAL_IP");
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail(h, CORAL_ERR_NOGPU, "no CUDA device: this library has no CPU fallback");
+    }
+    if (device < 0 || device >= count) return fail(h, CORAL_ERR_ARG, "device index out of range");
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(h, CORAL_ERR_CUDA, "cudaGetDeviceProperties failed");
+    }
+    if (prop.major != 10) return fail(h, CORAL_ERR_NOGPU, "kernels are built for sm_100a only");
+    h = new (std::nothrow) coral_index();
+    if (!h) return fail(nullptr, CORAL_ERR_CUDA, "out of host memory");
+    h->device = device;
+    h->sm_count = prop.multiProcessorCount;
+    h->smem_optin = (int)prop.sharedMemPerBlockOptin;
+    h->n = n;
+    h->dim = dim;
+    h->max_degree = max_degree;
+    h->deg_pad = max_degree <= 32 ? 32 : (max_degree <= 64 ? 64 : 128);
+    h->metric = metric;
+    cudaError_t e = cudaSetDevice(device);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreate(&h->ev_t0);
+    if (e == cudaSuccess) e = cudaEventCreate(&h->ev_k0);
+    if (e == cudaSuccess) e = cudaEventCreate(&h->ev_k1);
+    if (e == cudaSuccess) e = cudaEventCreate(&h->ev_t1);
+    if (e == cudaSuccess) e = cudaMalloc(&h->d_ctrl, 4 * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMallocHost(&h->h_ctrl, 4 * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMalloc(&h->d_hits, sizeof(int64_t));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        std::string msg = std::string("handle set-up: ") + cudaGetErrorString(e);
+        coral_index_destroy(h);
+        return fail(nullptr, CORAL_ERR_CUDA, msg);
+    }
+    *out = h;
+    return CORAL_OK;
+}
+
+int coral_index_destroy(coral_index_t* h) {
+    if (!h) return CORAL_OK;
+    cudaSetDevice(h->device);
+    if (h->stream) cudaStreamSynchronize(h->stream);
+    free_search(h);
+    if (h->own_vecs) cudaFree(h->d_vecs);
+    cudaFree(h->d_adj);
+    cudaFree(h->d_start);
+    cudaFree(h->d_deleted);
+    cudaFree(h->d_ctrl);
+    cudaFree(h->d_hits);
+    if (h->h_ctrl) cudaFreeHost(h->h_ctrl);
+    if (h->ev_t0) cudaEventDestroy(h->ev_t0);
+    if (h->ev_k0) cudaEventDestroy(h->ev_k0);
+    if (h->ev_k1) cudaEventDestroy(h->ev_k1);
+    if (h->ev_t1) cudaEventDestroy(h->ev_t1);
+    if (h->stream) cudaStreamDestroy(h->stream);
+    cudaGetLastError();
+    delete h;
+    return CORAL_OK;
+}
+
+int coral_index_set_vectors(coral_index_t* h, const float* vecs) {
+    if (!h || !vecs) return fail(h, CORAL_ERR_ARG, "null argument");
+    if (int rc = ensure_device(h)) return rc;
+    const size_t bytes = (size_t)h->n * h->dim * sizeof(float);
+    if (h->own_vecs) cudaFree(h->d_vecs);
+    h->d_vecs = nullptr;
+    h->own_vecs = false;
+    CK(cudaMalloc(&h->d_vecs, bytes));
+    h->own_vecs = true;
+    CK(cudaMemcpyAsync(h->d_vecs, vecs, bytes, cudaMemcpyDefault, h->stream));
+    CK(cudaStreamSynchronize(h->stream));
+    return CORAL_OK;
+}
+
+int coral_index_attach_vectors(coral_index_t* h, const float* dev_vecs) {
+    if (!h || !dev_vecs) return fail(h, CORAL_ERR_ARG, "null argument");
+    if (((uintptr_t)dev_vecs & 15) != 0) return fail(h, CORAL_ERR_ARG, "vectors must be 16-byte aligned");
+    if (!is_device_ptr(dev_vecs)) return fail(h, CORAL_ERR_ARG, "attach needs a device pointer");
+    if (int rc = ensure_device(h)) return rc;
+    if (h->own_vecs) cudaFree(h->d_vecs);
+    h->d_vecs = const_cast<float*>(dev_vecs);
+    h->own_vecs = false;
+    return CORAL_OK;
+}
+
+int coral_index_set_adjacency(coral_index_t* h, const int32_t* adj, int deg_pad) {
+    if (!h || !adj) return fail(h, CORAL_ERR_ARG, "null argument");
+    if (deg_pad != h->deg_pad) return fail(h, CORAL_ERR_ARG, "deg_pad must be max_degree rounded up to 32/64/128");
+    if (int rc = ensure_device(h)) return rc;
+    const size_t bytes = (size_t)h->n * deg_pad * sizeof(int32_t);
+    if (!h->d_adj) CK(cudaMalloc(&h->d_adj, bytes));
+    CK(cudaMemcpyAsync(h->d_adj, adj, bytes, cudaMemcpyDefault, h->stream));
+    CK(cudaStreamSynchronize(h->stream));
+    return CORAL_OK;
+}
+
+int coral_index_set_slots(coral_index_t* h, const int32_t* degs, size_t deg_stride, const int32_t* nbrs,
+                          size_t nbr_stride) {
+    if (!h || !degs || !nbrs || deg_stride == 0 || nbr_stride == 0) return fail(h, CORAL_ERR_ARG, "null argument");
+    std::vector<int32_t> adj((size_t)h->n * h->deg_pad, -1);
+    for (int64_t i = 0; i < h->n; ++i) {
+        int deg = degs[(size_t)i * deg_stride];
+        if (deg < 0) deg = 0;
+        if (deg > h->max_degree) deg = h->max_degree;  // src/graph.cu:723-727
+        const int32_t* nb = nbrs + (size_t)i * nbr_stride;
+        int32_t* row = adj.data() + (size_t)i * h->deg_pad;
+        int w = 0;
+        for (int j = 0; j < deg; ++j)
+            if (nb[j] >= 0 && (int64_t)nb[j] < h->n) row[w++] = nb[j];
+    }
+    return coral_index_set_adjacency(h, adj.data(), h->deg_pad);
+}
+
+int coral_index_set_start_ids(coral_index_t* h, const int32_t* ids, int M) {
+    if (!h || !ids || M <= 0 || M > 4096) return fail(h, CORAL_ERR_ARG, "start ids: need 1..4096 ids");
+    for (int i = 0; i < M; ++i)
+        if (ids[i] < 0 || (int64_t)ids[i] >= h->n) return fail(h, CORAL_ERR_ARG, "start id out of range");
+    if (int rc = ensure_device(h)) return rc;
+    cudaFree(h->d_start);
+    h->d_start = nullptr;
+    CK(cudaMalloc(&h->d_start, (size_t)M * sizeof(int32_t)));
+    CK(cudaMemcpyAsync(h->d_start, ids, (size_t)M * sizeof(int32_t), cudaMemcpyHostToDevice, h->stream));
+    CK(cudaStreamSynchronize(h->stream));
+    h->M = M;
+    return CORAL_OK;
+}
+
+int coral_index_set_deleted(coral_index_t* h, const uint32_t* bits) {
+    if (!h) return CORAL_ERR_ARG;
+    if (int rc = ensure_device(h)) return rc;
+    if (!bits) {
+        cudaFree(h->d_deleted);
+        h->d_deleted = nullptr;
+        return CORAL_OK;
+    }
+    const size_t bytes = (size_t)((h->n + 31) / 32) * sizeof(uint32_t);
+    if (!h->d_deleted) CK(cudaMalloc(&h->d_deleted, bytes));
+    CK(cudaMemcpyAsync(h->d_deleted, bits, bytes, cudaMemcpyDefault, h->stream));
+    CK(cudaStreamSynchronize(h->stream));
+    return CORAL_OK;
+}
+
+int coral_set_option(coral_index_t* h, const char* name, int value) {
+    if (!h || !name) return CORAL_ERR_ARG;
+    Options& o = h->opt;
+    std::string s(name);
+    if (s == "ctas_per_sm") o.ctas_per_sm = value;
+    else if (s == "warps") o.warps = value;
+    else if (s == "chunk_bytes") o.chunk_bytes = value;
+    else if (s == "stages") o.stages = value;
+    else if (s == "smem_hash_bits") o.smem_hash_bits = value;
+    else if (s == "ghash_factor") o.ghash_factor = value;
+    else if (s == "ghash_entries") o.ghash_entries = value;
+    else if (s == "max_rounds") o.max_rounds = value;
+    else return fail(h, CORAL_ERR_ARG, "unknown option " + s);
+    h->plans.clear();
+    return CORAL_OK;
+}
+
+int coral_get_option(coral_index_t* h, const char* name, int* value) {
+    if (!h || !name || !value) return CORAL_ERR_ARG;
+    const Options& o = h->opt;
+    std::string s(name);
+    if (s == "ctas_per_sm") *value = o.ctas_per_sm;
+    else if (s == "warps") *value = o.warps;
+    else if (s == "chunk_bytes") *value = o.chunk_bytes;
+    else if (s == "stages") *value = o.stages;
+    else if (s == "smem_hash_bits") *value = o.smem_hash_bits;
+    else if (s == "ghash_factor") *value = o.ghash_factor;
+    else if (s == "ghash_entries") *value = (int)h->gh_entries;
+    else if (s == "max_rounds") *value = o.max_rounds;
+    else if (s == "grid_cap") *value = h->grid_cap;
+    else if (s == "deg_pad") *value = h->deg_pad;
+    else if (s.rfind("plan_", 0) == 0 && !h->plans.empty()) {  // plan of the most recent L
+        const SearchPlan& p = h->plans.rbegin()->second.first;
+        if (s == "plan_stages") *value = p.stages;
+        else if (s == "plan_chunk_bytes") *value = p.chunk_bytes;
+        else if (s == "plan_smem_bytes") *value = p.smem_bytes;
+        else if (s == "plan_hash_bits") *value = p.hs_bits;
+        else if (s == "plan_ctas_per_sm") *value = h->plans.rbegin()->second.second;
+        else return fail(h, CORAL_ERR_ARG, "unknown option " + s);
+    } else return fail(h, CORAL_ERR_ARG, "unknown option " + s);
+    return CORAL_OK;
+}
+
+int coral_search_free(coral_index_t* h) {
+    if (!h) return CORAL_ERR_ARG;
+    if (int rc = ensure_device(h)) return rc;
+    cudaStreamSynchronize(h->stream);
+    free_search(h);
+    return CORAL_OK;
+}
+
+int coral_search_prepare(coral_index_t* h, int max_queries, int max_L, int max_k) {
+    if (!h || max_queries <= 0 || max_L <= 0 || max_k <= 0 || max_k > max_L || max_L > 4096)
+        return fail(h, CORAL_ERR_ARG, "prepare: need max_queries > 0 and 0 < max_k <= max_L <= 4096");
+    if (int rc = ensure_device(h)) return rc;
+    cudaStreamSynchronize(h->stream);
+    free_search(h);
+    SearchPlan p;
+    int per_sm = 0;
+    if (int rc = get_plan(h, max_L, p, per_sm)) return rc;
+    // smaller L never needs more CTAs than ctas_per_sm allows
+    h->grid_cap = h->sm_count * std::max(per_sm, h->opt.ctas_per_sm);
+    h->max_q = max_queries;
+    h->max_L = max_L;
+    h->max_k = max_k;
+    uint64_t want = (uint64_t)std::max(h->opt.ghash_factor, 2) * (uint64_t)max_L * (uint64_t)h->deg_pad;
+    uint32_t ent = 1u << 14;
+    while (ent < want && ent < (1u << 24)) ent <<= 1;
+    if (h->opt.ghash_entries >= 64) {
+        ent = 64;
+        while (ent < (uint32_t)h->opt.ghash_entries && ent < (1u << 24)) ent <<= 1;
+    }
+    h->gh_entries = ent;
+    h->cand_cap_alloc = (size_t)max_L * h->deg_pad;
+    CK(cudaMalloc(&h->d_ghash, (size_t)h->grid_cap * ent * sizeof(uint64_t)));
+    CK(cudaMemsetAsync(h->d_ghash, 0, (size_t)h->grid_cap * ent * sizeof(uint64_t), h->stream));
+    h->epoch_base = 0;
+    CK(cudaMalloc(&h->d_gcand, (size_t)h->grid_cap * h->cand_cap_alloc * sizeof(uint64_t)));
+    CK(cudaMalloc(&h->d_queries, (size_t)max_queries * h->dim * sizeof(float)));
+    CK(cudaMalloc(&h->d_ids, (size_t)max_queries * max_k * sizeof(int32_t)));
+    CK(cudaMalloc(&h->d_dists, (size_t)max_queries * max_k * sizeof(float)));
+    CK(cudaMalloc(&h->d_stats, (size_t)max_queries * CORAL_STATS_W * sizeof(int32_t)));
+    CK(cudaStreamSynchronize(h->stream));
+    h->prepared = true;
+    return CORAL_OK;
+}
+
+static int enqueue_search(coral_index* h, const float* d_queries, int Q, int L, int k, int32_t* d_ids,
+                          float* d_dists, int32_t* d_stats, cudaStream_t st) {
+    if (!h->d_vecs || !h->d_adj || !h->d_start) return fail(h, CORAL_ERR_STATE, "vectors, graph and start ids must be set first");
+    if (!h->prepared) return fail(h, CORAL_ERR_STATE, "coral_search_prepare has not been called");
+    if (Q < 0 || L <= 0 || k <= 0 || k > L) return fail(h, CORAL_ERR_ARG, "need Q >= 0 and 0 < k <= L");
+    if (h->M > L) return fail(h, CORAL_ERR_ARG, "more start ids than beam capacity L");
+    if (Q > h->max_q || L > h->max_L || k > h->max_k) return fail(h, CORAL_ERR_LIMIT, "request exceeds coral_search_prepare sizes");
+    SearchPlan p;
+    int per_sm = 0;
+    if (int rc = get_plan(h, L, p, per_sm)) return rc;
+    CK(cudaMemsetAsync(h->d_ctrl, 0, 4 * sizeof(unsigned long long), st));
+    if (Q == 0) return CORAL_OK;
+    if ((uint64_t)h->epoch_base + (uint64_t)Q + 2ull >= 0xFFFFFFFFull) {  // epochs would wrap: start over
+        CK(cudaMemsetAsync(h->d_ghash, 0, (size_t)h->grid_cap * h->gh_entries * sizeof(uint64_t), st));
+        h->epoch_base = 0;
+    }
+    SearchArgs a{};
+    a.vecs = h->d_vecs;
+    a.adj = h->d_adj;
+    a.queries = d_queries;
+    a.start_ids = h->d_start;
+    a.deleted = h->d_deleted;
+    a.ids_out = d_ids;
+    a.dists_out = d_dists;
+    a.stats_out = d_stats;
+    a.q_counter = reinterpret_cast<int*>(h->d_ctrl);
+    a.err_flag = reinterpret_cast<int*>(h->d_ctrl) + 1;
+    a.hops_total = h->d_ctrl + 1;
+    a.ghash = h->d_ghash;
+    a.gcand = h->d_gcand;
+    a.n = h->n;
+    a.dim = h->dim;
+    a.deg_pad = h->deg_pad;
+    a.deg_shift = h->deg_pad == 32 ? 5 : (h->deg_pad == 64 ? 6 : 7);
+    a.M = h->M;
+    a.Q = Q;
+    a.L = L;
+    a.k = k;
+    a.epoch_base = h->epoch_base;
+    a.gh_mask = h->gh_entries - 1;
+    a.cand_cap = (int)std::min<size_t>((size_t)L * h->deg_pad, h->cand_cap_alloc);
+    a.max_rounds = h->opt.max_rounds;
+    a.plan = p;
+    const int grid = std::min(Q, std::min(h->sm_count * per_sm, h->grid_cap));
+    CK(coral::launch_beam_search(a, h->metric, grid, st));
+    h->launches += 1;
+    h->epoch_base += (uint32_t)Q;
+    CK(cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, st));
+    return CORAL_OK;
+}
+
+int coral_search_async(coral_index_t* h, const float* d_queries, int Q, int L, int k, int32_t* d_ids_out,
+                       float* d_dists_out, int32_t* d_stats_out, void* stream) {
+    if (!h || (!d_queries && Q > 0) || (!d_ids_out && Q > 0)) return fail(h, CORAL_ERR_ARG, "null argument");
+    if (int rc = ensure_device(h)) return rc;
+    cudaStream_t st = stream ? (cudaStream_t)stream : h->stream;
+    return enqueue_search(h, d_queries, Q, L, k, d_ids_out, d_dists_out, d_stats_out, st);
+}
+
+int coral_search_check(coral_index_t* h) {
+    if (!h) return CORAL_ERR_ARG;
+    const int err = reinterpret_cast<int*>(h->h_ctrl)[1];
+    if (err) return fail(h, CORAL_ERR_KERNEL, "a bounded wait in the search kernel ran out; results are invalid");
+    return CORAL_OK;
+}
+
+int coral_search(coral_index_t* h, const float* queries, int Q, int L, int k, int32_t* ids_out,
+                 float* dists_out, int32_t* stats_out, int64_t* total_hops_out) {
+    if (!h || (Q > 0 && (!queries || !ids_out))) return fail(h, CORAL_ERR_ARG, "null argument");
+    if (int rc = ensure_device(h)) return rc;
+    if (!h->prepared) return fail(h, CORAL_ERR_STATE, "coral_search_prepare has not been called");
+    if (Q > h->max_q || k > h->max_k) return fail(h, CORAL_ERR_LIMIT, "request exceeds coral_search_prepare sizes");
+    cudaStream_t st = h->stream;
+    const bool q_dev = Q > 0 && is_device_ptr(queries);
+    const bool i_dev = Q > 0 && is_device_ptr(ids_out);
+    const bool d_dev = dists_out && is_device_ptr(dists_out);
+    const bool s_dev = stats_out && is_device_ptr(stats_out);
+    const float* dq = q_dev ? queries : h->d_queries;
+    int32_t* di = i_dev ? ids_out : h->d_ids;
+    float* dd = dists_out ? (d_dev ? dists_out : h->d_dists) : nullptr;
+    int32_t* ds = stats_out ? (s_dev ? stats_out : h->d_stats) : nullptr;
+
+    CK(cudaEventRecord(h->ev_t0, st));
+    if (Q > 0 && !q_dev)
+        CK(cudaMemcpyAsync(h->d_queries, queries, (size_t)Q * h->dim * sizeof(float), cudaMemcpyHostToDevice, st));
+    CK(cudaEventRecord(h->ev_k0, st));
+    if (int rc = enqueue_search(h, dq, Q, L, k, di, dd, ds, st)) return rc;
+    CK(cudaEventRecord(h->ev_k1, st));
+    if (Q > 0) {
+        if (!i_dev) CK(cudaMemcpyAsync(ids_out, di, (size_t)Q * k * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+        if (dists_out && !d_dev)
+            CK(cudaMemcpyAsync(dists_out, dd, (size_t)Q * k * sizeof(float), cudaMemcpyDeviceToHost, st));
+        if (stats_out && !s_dev)
+            CK(cudaMemcpyAsync(stats_out, ds, (size_t)Q * CORAL_STATS_W * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+    }
+    CK(cudaEventRecord(h->ev_t1, st));
+    CK(cudaStreamSynchronize(st));
+    CK(cudaEventElapsedTime(&h->last_kernel_ms, h->ev_k0, h->ev_k1));
+    CK(cudaEventElapsedTime(&h->last_total_ms, h->ev_t0, h->ev_t1));
+    if (total_hops_out) *total_hops_out = Q > 0 ? (int64_t)h->h_ctrl[1] : 0;
+    if (Q > 0)
+        if (int rc = coral_search_check(h)) return rc;
+    return CORAL_OK;
+}
+
+float coral_last_kernel_ms(coral_index_t* h) { return h ? h->last_kernel_ms : 0.f; }
+float coral_last_total_ms(coral_index_t* h) { return h ? h->last_total_ms : 0.f; }
+int64_t coral_launch_count(coral_index_t* h) { return h ? h->launches : 0; }
+
+int coral_count_hits(coral_index_t* h, const int32_t* res, const int32_t* gt, int Q, int k, int gt_dim,
+                     int64_t* hits_out) {
+    if (!h || !res || !gt || !hits_out || Q < 0 || k <= 0 || gt_dim < k) return fail(h, CORAL_ERR_ARG, "bad argument");
+    if (int rc = ensure_device(h)) return rc;
+    *hits_out = 0;
+    if (Q == 0) return CORAL_OK;
+    cudaStream_t st = h->stream;
+    int32_t *d_res = nullptr, *d_gt = nullptr;
+    const bool r_dev = is_device_ptr(res), g_dev = is_device_ptr(gt);
+    int rc = CORAL_OK;
+    cudaError_t e = cudaSuccess;
+    if (!r_dev) {
+        e = cudaMalloc(&d_res, (size_t)Q * k * 4);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(d_res, res, (size_t)Q * k * 4, cudaMemcpyHostToDevice, st);
+    }
+    if (e == cudaSuccess && !g_dev) {
+        e = cudaMalloc(&d_gt, (size_t)Q * gt_dim * 4);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(d_gt, gt, (size_t)Q * gt_dim * 4, cudaMemcpyHostToDevice, st);
+    }
+    if (e == cudaSuccess) e = cudaMemsetAsync(h->d_hits, 0, sizeof(int64_t), st);
+    if (e == cudaSuccess) {
+        const int blocks = (int)std::min<long long>(((long long)Q * k + 255) / 256, 4096);
+        count_hits_kernel<<<blocks, 256, 0, st>>>(r_dev ? res : d_res, g_dev ? gt : d_gt, Q, k, gt_dim,
+                                                  reinterpret_cast<unsigned long long*>(h->d_hits));
+        h->launches += 1;
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(hits_out, h->d_hits, sizeof(int64_t), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        rc = fail(h, CORAL_ERR_CUDA, std::string("count_hits: ") + cudaGetErrorString(e));
+    }
+    cudaFree(d_res);
+    cudaFree(d_gt);
+    return rc;
+}
+
+int coral_merge_shards(coral_index_t* h, const int32_t* d_ids, const float* d_dists, int G, int Q, int k,
+                       int32_t* d_ids_out, float* d_dists_out, void* stream) {
+    if (!h || !d_ids || !d_dists || !d_ids_out || !d_dists_out || G <= 0 || Q < 0 || k <= 0)
+        return fail(h, CORAL_ERR_ARG, "bad argument");
+    if ((long long)G * k > 4096) return fail(h, CORAL_ERR_LIMIT, "G*k must not exceed 4096");
+    if (int rc = ensure_device(h)) return rc;
+    if (Q == 0) return CORAL_OK;
+    cudaStream_t st = stream ? (cudaStream_t)stream : h->stream;
+    const int n2 = next_pow2(std::max(G * k, 32));
+    const int wpb = std::max(1, std::min(8, 8192 / n2));
+    const size_t smem = (size_t)wpb * n2 * 8;
+    CK(cudaFuncSetAttribute(merge_shards_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int blocks = std::min((Q + wpb - 1) / wpb, h->sm_count * 8);
+    merge_shards_kernel<<<blocks, wpb * 32, smem, st>>>(d_ids, d_dists, G, Q, k, n2, h->metric, d_ids_out, d_dists_out);
+    h->launches += 1;
+    CK(cudaGetLastError());
+    return CORAL_OK;
+}
+
+int coral_map_ids(coral_index_t* h, int32_t* d_ids, int64_t count, const int32_t* d_id_map, void* stream) {
+    if (!h || !d_ids || !d_id_map || count < 0) return fail(h, CORAL_ERR_ARG, "bad argument");
+    if (int rc = ensure_device(h)) return rc;
+    if (count == 0) return CORAL_OK;
+    cudaStream_t st = stream ? (cudaStream_t)stream : h->stream;
+    const int blocks = (int)std::min<long long>((count + 255) / 256, (long long)h->sm_count * 16);
+    map_ids_kernel<<<blocks, 256, 0, st>>>(d_ids, count, d_id_map);
+    h->launches += 1;
+    CK(cudaGetLastError());
+    return CORAL_OK;
+}
+
+}  // extern "C"

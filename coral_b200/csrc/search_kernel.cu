@@ -1,0 +1,620 @@
+// Batched "full expansion" graph beam search for sm_100a.
+//
+// One CTA owns one query at a time (queries are pulled from an atomic counter,
+// like the reference's persistent blocks, src/search_gpu.cu:379).  Inside a
+// round every warp is an autonomous pipeline:
+//
+//   scout    read the adjacency rows of beam entries still to be expanded
+//            (coalesced, 128 neighbour ids per step), test-and-set each id in
+//            the exact visited set (shared-memory hash, spilling to an
+//            epoch-tagged global table), keep the new ids;
+//   gather   for 32 new ids at a time, bring the rows into shared memory chunk
+//            by chunk with one bulk asynchronous copy (cp.async.bulk, completion
+//            counted on an mbarrier) per row chunk, several stages in flight;
+//   distance lane j owns row j and accumulates over the chunks in the order of
+//            the reference's thread-per-neighbour loop (include/utils.cuh:254-275,
+//            :307-323): one sequential fp32 fused chain over d = 0..dim-1, so the
+//            distance is bit-identical to the reference's;
+//   filter   strictly closer than the worst beam distance at round start
+//            (src/search_gpu.cu:432) -> appended to the CTA's candidate buffer.
+//
+// At the end of a round the CTA merges beam and candidates into the L closest,
+// kept sorted by (distance, id): candidates are sorted tile by tile (bitonic, in
+// the idle staging memory) and merged by rank.  This replaces the reference's
+// one-reduction-per-accepted-candidate loop (src/search_gpu.cu:525-570) and
+// yields the same set; ties are resolved by id instead of by thread position.
+//
+// Nothing here traps or spins without bound: every mbarrier wait has a clock
+// limit after which an error flag is raised and the CTA stops taking queries.
+#include "search_kernel.cuh"
+
+namespace coral {
+
+namespace {
+
+constexpr int kPendCap = 160;   // new ids waiting for a gather batch: < 32 left over + 128 per scout step
+constexpr int kIdsPerLane = 4;  // neighbour ids examined per lane per scout step
+constexpr int kSmemProbes = 8;
+constexpr int kGlobalProbes = 256;
+constexpr uint32_t kEmpty32 = 0xFFFFFFFFu;
+constexpr uint64_t kPadKey = 0xFFFFFFFFFFFFFFFFull;
+constexpr long long kWaitClocks = 4000000000ll;  // ~2 s: far beyond any legitimate copy latency
+
+struct Control {
+    int qid;
+    int exp_count;
+    int exp_next;
+    int cand_count;
+    int beam_cnt;
+    int fill;
+    int status;
+    float worst;
+    // per-query counters
+    int n_dist, n_exp, n_scan, n_spill, hops, rounds, max_cand;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Bounded wait: returns false (and raises *err) when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > kWaitClocks) {
+            atomicExch(err, 1);
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// "closer" == smaller key.  key = ord(dist):id:expanded-bit.
+template <int METRIC>
+__device__ __forceinline__ uint32_t ord_of(float d) {
+    if (METRIC == 1) d = -d;
+    uint32_t u = __float_as_uint(d);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+template <int METRIC>
+__device__ __forceinline__ float dist_of(uint32_t o) {
+    uint32_t u = (o & 0x80000000u) ? (o & 0x7fffffffu) : ~o;
+    float d = __uint_as_float(u);
+    return METRIC == 1 ? -d : d;
+}
+template <int METRIC>
+__device__ __forceinline__ uint64_t make_key(float d, int id, uint32_t expanded) {
+    return ((uint64_t)ord_of<METRIC>(d) << 32) | ((uint64_t)(uint32_t)id << 1) | (uint64_t)expanded;
+}
+__device__ __forceinline__ int key_id(uint64_t k) { return (int)((uint32_t)(k & 0xffffffffu) >> 1); }
+
+// include/utils.cuh:380-382 with d0 = worst: true when d is strictly closer.
+template <int METRIC>
+__device__ __forceinline__ bool closer_than(float worst, float d) {
+    return METRIC == 0 ? worst > d : worst < d;
+}
+
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+    x ^= x >> 16;
+    x *= 0x7feb352du;
+    x ^= x >> 15;
+    x *= 0x846ca68bu;
+    x ^= x >> 16;
+    return x;
+}
+
+// Exact test-and-set.  0 = newly inserted, 1 = already present, 2 = tables full.
+// A key lives in the shared table iff its probe window had a free slot when it
+// first arrived; windows never lose entries within a query, so a later lookup
+// takes the same route.
+__device__ __forceinline__ int visited_insert(uint32_t* sh, int hs_bits, uint64_t* gh, uint32_t gmask,
+                                              uint32_t epoch, int id, int& n_spill) {
+    if (hs_bits > 0) {
+        const uint32_t mask = (1u << hs_bits) - 1u;
+        const uint32_t h = ((uint32_t)id * 0x9E3779B1u) >> (32 - hs_bits);
+#pragma unroll 1
+        for (int p = 0; p < kSmemProbes; ++p) {
+            const uint32_t old = atomicCAS(&sh[(h + p) & mask], kEmpty32, (uint32_t)id);
+            if (old == kEmpty32) return 0;
+            if (old == (uint32_t)id) return 1;
+        }
+    }
+    const uint64_t mine = ((uint64_t)epoch << 32) | (uint32_t)id;
+    const uint32_t h = mix32((uint32_t)id);
+#pragma unroll 1
+    for (int p = 0; p < kGlobalProbes; ++p) {
+        unsigned long long* slot = (unsigned long long*)&gh[(h + p) & gmask];
+        unsigned long long cur = *(volatile unsigned long long*)slot;
+        for (;;) {
+            if ((uint32_t)(cur >> 32) == epoch) {
+                if ((uint32_t)cur == (uint32_t)id) return 1;
+                break;  // taken by another id of this query: next slot
+            }
+            const unsigned long long old = atomicCAS(slot, cur, (unsigned long long)mine);
+            if (old == cur) {
+                ++n_spill;
+                return 0;
+            }
+            cur = old;
+        }
+    }
+    return 2;
+}
+
+// CTA-wide bitonic sort of n (power of two) keys in shared memory, ascending.
+__device__ void bitonic_sort(uint64_t* s, int n, int tid, int nthreads) {
+    for (int k = 2; k <= n; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = tid; i < n; i += nthreads) {
+                const int ixj = i ^ j;
+                if (ixj > i) {
+                    const uint64_t a = s[i], b = s[ixj];
+                    const bool asc = (i & k) == 0;
+                    if ((a > b) == asc) {
+                        s[i] = b;
+                        s[ixj] = a;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+__device__ __forceinline__ int lower_bound_u64(const uint64_t* a, int n, uint64_t x) {  // #{a[i] < x}
+    int lo = 0, hi = n;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (a[mid] < x)
+            lo = mid + 1;
+        else
+            hi = mid;
+    }
+    return lo;
+}
+__device__ __forceinline__ int upper_bound_u64(const uint64_t* a, int n, uint64_t x) {  // #{a[i] <= x}
+    int lo = 0, hi = n;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (a[mid] <= x)
+            lo = mid + 1;
+        else
+            hi = mid;
+    }
+    return lo;
+}
+
+// One sequential fused chain over a chunk: row and query both in shared memory.
+template <int METRIC>
+__device__ __forceinline__ float accumulate_chunk(float acc, const float4* __restrict__ row,
+                                                  const float4* __restrict__ q, int n_vec) {
+#pragma unroll 4
+    for (int i = 0; i < n_vec; ++i) {
+        const float4 a = row[i];
+        const float4 b = q[i];
+        if (METRIC == 0) {
+            float d;
+            d = a.x - b.x; acc = fmaf(d, d, acc);
+            d = a.y - b.y; acc = fmaf(d, d, acc);
+            d = a.z - b.z; acc = fmaf(d, d, acc);
+            d = a.w - b.w; acc = fmaf(d, d, acc);
+        } else {
+            acc = fmaf(a.x, b.x, acc);
+            acc = fmaf(a.y, b.y, acc);
+            acc = fmaf(a.z, b.z, acc);
+            acc = fmaf(a.w, b.w, acc);
+        }
+    }
+    return acc;
+}
+
+// Seed distance in the order of src/search_gpu.cu:14-23: lane-strided fused
+// chains, then sum += shfl_down(sum, off) for off = 16..1; lane 0 holds it.
+template <int METRIC>
+__device__ __forceinline__ float seed_distance(const float* __restrict__ row, const float* __restrict__ q,
+                                               int dim, int lane) {
+    float sum = 0.f;
+    for (int d = lane; d < dim; d += 32) {
+        const float b = __ldg(row + d);
+        if (METRIC == 0) {
+            const float diff = q[d] - b;
+            sum = fmaf(diff, diff, sum);
+        } else {
+            sum = fmaf(q[d], b, sum);
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum = sum + __shfl_down_sync(0xffffffffu, sum, off);
+    return __shfl_sync(0xffffffffu, sum, 0);
+}
+
+template <int METRIC>
+__global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ Control S;
+
+    const SearchPlan& P = a.plan;
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const uint32_t lt_mask = (1u << lane) - 1u;
+
+    float* sq = reinterpret_cast<float*>(smem + P.off_query);
+    uint64_t* beam = reinterpret_cast<uint64_t*>(smem + P.off_beam0);
+    uint64_t* beam_alt = reinterpret_cast<uint64_t*>(smem + P.off_beam1);
+    int* exp_list = reinterpret_cast<int*>(smem + P.off_exp);
+    uint32_t* shash = reinterpret_cast<uint32_t*>(smem + P.off_hash);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P.off_bar) + warp * P.stages;
+    int* pend = reinterpret_cast<int*>(smem + P.off_pend) + warp * kPendCap;
+    int* bids = reinterpret_cast<int*>(smem + P.off_bids) + warp * 64;  // two batch slots of 32 ids
+    unsigned char* stage0 = smem + P.off_stage + (size_t)warp * P.stages * P.stage_bytes;
+    uint64_t* sortbuf = reinterpret_cast<uint64_t*>(smem + P.off_stage);  // aliases the staging rings
+
+    uint64_t* ghash = a.ghash + (size_t)blockIdx.x * ((size_t)a.gh_mask + 1);
+    uint64_t* gcand = a.gcand + (size_t)blockIdx.x * (size_t)a.cand_cap;
+
+    if (lane == 0)
+        for (int s = 0; s < P.stages; ++s) mbar_init(&bars[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+    __syncthreads();
+
+    // chunk stream positions of this warp; monotonic over the kernel's life so
+    // that the parity of use u of a stage is u & 1.
+    uint32_t iss = 0, con = 0;
+    const int n_chunks = P.n_chunks;
+    const int chunk_vec = P.chunk_bytes >> 4;
+    const int chunk_floats = P.chunk_bytes >> 2;
+    const int G = 128 >> a.deg_shift;  // beam entries covered by one scout step
+    const int row_bytes = a.dim * 4;
+
+    for (;;) {
+        // ---------------------------------------------------------------- take a query
+        __syncthreads();
+        if (tid == 0) {
+            int q = -1;
+            if (*(volatile int*)a.err_flag == 0) q = atomicAdd(a.q_counter, 1);
+            if (q >= a.Q) q = -1;
+            S.qid = q;
+            S.status = 0;
+            S.worst = METRIC == 0 ? 3.402823466e+38f : -3.402823466e+38f;
+            S.n_dist = a.M;
+            S.n_exp = S.n_scan = S.n_spill = S.hops = S.rounds = S.max_cand = 0;
+            S.beam_cnt = a.M;
+        }
+        __syncthreads();
+        const int qid = S.qid;
+        if (qid < 0) break;
+        const uint32_t epoch = a.epoch_base + (uint32_t)qid + 1u;
+
+        for (int d = tid; d < a.dim; d += nthreads) sq[d] = a.queries[(size_t)qid * a.dim + d];
+        if (P.hs_bits > 0)
+            for (int i = tid; i < (1 << P.hs_bits); i += nthreads) shash[i] = kEmpty32;
+        for (int i = tid; i < P.LP; i += nthreads) beam[i] = kPadKey;
+        __syncthreads();
+
+        int n_spill = 0, n_scan = 0, n_exp = 0, n_dist = 0;  // per-thread tallies
+        bool overflow = false;
+
+        // ---------------------------------------------------------------- entry points
+        for (int i = warp; i < a.M; i += (nthreads >> 5)) {
+            const int id = a.start_ids[i];
+            if (lane == 0) {
+                const int r = visited_insert(shash, P.hs_bits, ghash, a.gh_mask, epoch, id, n_spill);
+                if (r == 2) overflow = true;  // duplicates are kept on purpose (src/search_gpu.cu:396-397)
+            }
+            const float d = seed_distance<METRIC>(a.vecs + (size_t)id * a.dim, sq, a.dim, lane);
+            if (lane == 0) beam[i] = make_key<METRIC>(d, id, 0u);
+        }
+        __syncthreads();
+        bitonic_sort(beam, P.LP, tid, nthreads);
+
+        // ---------------------------------------------------------------- rounds
+        for (;;) {
+            // expansion list: every beam entry not yet expanded (src/search_gpu.cu:416-422)
+            if (tid == 0) {
+                S.exp_count = 0;
+                S.exp_next = 0;
+                S.cand_count = 0;
+                S.rounds += 1;
+            }
+            __syncthreads();
+            const int beam_cnt = S.beam_cnt;
+            for (int i = tid; i < beam_cnt; i += nthreads) {
+                const uint64_t key = beam[i];
+                if ((key & 1ull) == 0ull) {
+                    exp_list[atomicAdd(&S.exp_count, 1)] = key_id(key);
+                    beam[i] = key | 1ull;
+                }
+            }
+            __syncthreads();
+            const int exp_count = S.exp_count;
+            const float worst = S.worst;
+
+            // ------------------------------------------------------------ warp pipeline
+            {
+                int pend_n = 0;
+                uint32_t formed = iss / n_chunks;  // batches formed so far (== consumed here)
+                uint32_t done = formed;            // batches finalised
+                int bcnt0 = 0, bcnt1 = 0;          // rows in batch slot 0 / 1
+                bool more = exp_count > 0;
+                float acc = 0.f;
+                for (;;) {
+                    // form gather batches from pending ids
+                    while (formed - done < 2u && (pend_n >= 32 || (!more && pend_n > 0))) {
+                        const int m = pend_n < 32 ? pend_n : 32;
+                        const int slot = formed & 1u;
+                        if (lane < m) bids[slot * 32 + lane] = pend[pend_n - m + lane];
+                        if (slot) bcnt1 = m; else bcnt0 = m;
+                        pend_n -= m;
+                        ++formed;
+                        __syncwarp();
+                    }
+                    // keep the ring full
+                    while (iss < formed * (uint32_t)n_chunks && iss - con < (uint32_t)P.stages) {
+                        const uint32_t b = iss / n_chunks, c = iss - b * n_chunks, st = iss % P.stages;
+                        const int cnt = (b & 1u) ? bcnt1 : bcnt0;
+                        if (lane == 0) mbar_expect_tx(&bars[st], (uint32_t)cnt * (uint32_t)P.chunk_bytes);
+                        __syncwarp();
+                        if (lane < cnt) {
+                            const int id = bids[(b & 1u) * 32 + lane];
+                            bulk_g2s(stage0 + (size_t)st * P.stage_bytes + (size_t)lane * P.row_stride,
+                                     reinterpret_cast<const unsigned char*>(a.vecs) + (size_t)id * row_bytes +
+                                         (size_t)c * P.chunk_bytes,
+                                     (uint32_t)P.chunk_bytes, &bars[st]);
+                        }
+                        ++iss;
+                    }
+                    if (more && pend_n < 32) {
+                        // ---- scout: adjacency rows of up to G entries, visited test-and-set
+                        int e0 = 0;
+                        if (lane == 0) e0 = atomicAdd(&S.exp_next, G);
+                        e0 = __shfl_sync(0xffffffffu, e0, 0);
+                        if (e0 >= exp_count) {
+                            more = false;
+                            continue;
+                        }
+                        if (lane == 0) n_exp += (exp_count - e0 < G) ? exp_count - e0 : G;
+                        int v[kIdsPerLane];
+#pragma unroll
+                        for (int t = 0; t < kIdsPerLane; ++t) {
+                            const int slot = lane + 32 * t;
+                            const int ent = e0 + (slot >> a.deg_shift);
+                            v[t] = -1;
+                            if (ent < exp_count)
+                                v[t] = __ldg(a.adj + (size_t)exp_list[ent] * a.deg_pad + (slot & (a.deg_pad - 1)));
+                        }
+                        bool isnew[kIdsPerLane];
+#pragma unroll
+                        for (int t = 0; t < kIdsPerLane; ++t) {
+                            isnew[t] = false;
+                            if (v[t] >= 0 && (int64_t)v[t] < a.n) {
+                                ++n_scan;
+                                const int r =
+                                    visited_insert(shash, P.hs_bits, ghash, a.gh_mask, epoch, v[t], n_spill);
+                                isnew[t] = (r == 0);
+                                if (r == 2) overflow = true;
+                            }
+                        }
+#pragma unroll
+                        for (int t = 0; t < kIdsPerLane; ++t) {
+                            const uint32_t m = __ballot_sync(0xffffffffu, isnew[t]);
+                            if (isnew[t]) pend[pend_n + __popc(m & lt_mask)] = v[t];
+                            pend_n += __popc(m);
+                        }
+                        __syncwarp();
+                        continue;
+                    }
+                    if (con < iss) {
+                        // ---- distance: one chunk of the oldest batch in flight
+                        const uint32_t b = con / n_chunks, c = con - b * n_chunks, st = con % P.stages;
+                        const int cnt = (b & 1u) ? bcnt1 : bcnt0;
+                        mbar_wait(&bars[st], (con / P.stages) & 1u, a.err_flag);
+                        if (c == 0) acc = 0.f;
+                        if (lane < cnt)
+                            acc = accumulate_chunk<METRIC>(
+                                acc,
+                                reinterpret_cast<const float4*>(stage0 + (size_t)st * P.stage_bytes +
+                                                                (size_t)lane * P.row_stride),
+                                reinterpret_cast<const float4*>(sq + (size_t)c * chunk_floats), chunk_vec);
+                        fence_async_smem();
+                        __syncwarp();
+                        ++con;
+                        if (c == (uint32_t)n_chunks - 1u) {
+                            // ---- filter and emit (src/search_gpu.cu:431-434)
+                            const bool ok = lane < cnt && closer_than<METRIC>(worst, acc);
+                            const uint32_t m = __ballot_sync(0xffffffffu, ok);
+                            int base = 0;
+                            if (lane == 0) {
+                                n_dist += cnt;
+                                if (m) base = atomicAdd(&S.cand_count, __popc(m));
+                            }
+                            base = __shfl_sync(0xffffffffu, base, 0);
+                            if (ok) {
+                                const int pos = base + __popc(m & lt_mask);
+                                if (pos < a.cand_cap)
+                                    gcand[pos] = make_key<METRIC>(acc, bids[(b & 1u) * 32 + lane], 0u);
+                            }
+                            ++done;
+                            __syncwarp();
+                        }
+                        continue;
+                    }
+                    if (!more && pend_n == 0) break;
+                }
+            }
+            __syncthreads();
+
+            // ------------------------------------------------------------ merge
+            int C = S.cand_count;
+            if (C > a.cand_cap) C = a.cand_cap;
+            if (C == 0) break;  // converged (src/search_gpu.cu:442)
+            int cnt = S.beam_cnt;
+            const bool over = cnt + C > a.L;
+            uint64_t bound = cnt >= a.L ? beam[a.L - 1] : kPadKey;
+            int pos = 0;
+            while (pos < C) {
+                if (tid == 0) S.fill = 0;
+                __syncthreads();
+                int fill = 0;
+                while (pos < C && fill + nthreads <= P.tile_max) {
+                    const int i = pos + tid;
+                    if (i < C) {
+                        const uint64_t key = gcand[i];
+                        if (key < bound) sortbuf[atomicAdd(&S.fill, 1)] = key;
+                    }
+                    pos += nthreads;
+                    __syncthreads();
+                    fill = S.fill;
+                }
+                if (fill == 0) continue;
+                int n2 = 32;
+                while (n2 < fill) n2 <<= 1;
+                for (int i = fill + tid; i < n2; i += nthreads) sortbuf[i] = kPadKey;
+                __syncthreads();
+                bitonic_sort(sortbuf, n2, tid, nthreads);
+                // merge by rank: beam[0..cnt) and sortbuf[0..fill), both ascending, keys distinct
+                for (int i = tid; i < cnt; i += nthreads) {
+                    const uint64_t x = beam[i];
+                    const int p = i + lower_bound_u64(sortbuf, fill, x);
+                    if (p < a.L) beam_alt[p] = x;
+                }
+                for (int j = tid; j < fill; j += nthreads) {
+                    const uint64_t x = sortbuf[j];
+                    const int p = j + upper_bound_u64(beam, cnt, x);
+                    if (p < a.L) beam_alt[p] = x;
+                }
+                cnt = cnt + fill < a.L ? cnt + fill : a.L;
+                for (int i = cnt + tid; i < P.LP; i += nthreads) beam_alt[i] = kPadKey;
+                __syncthreads();
+                uint64_t* t = beam;
+                beam = beam_alt;
+                beam_alt = t;
+                if (cnt >= a.L) bound = beam[a.L - 1];
+            }
+            if (tid == 0) {
+                S.hops += C;                          // src/search_gpu.cu:481,574
+                if (C > S.max_cand) S.max_cand = C;
+                S.beam_cnt = cnt;
+                if (over) S.worst = dist_of<METRIC>((uint32_t)(beam[a.L - 1] >> 32));  // :573
+                if (S.rounds >= a.max_rounds) S.status = 3;
+            }
+            __syncthreads();
+            if (S.status == 3) break;
+        }
+
+        // ---------------------------------------------------------------- tallies
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            n_scan += __shfl_down_sync(0xffffffffu, n_scan, off);
+            n_spill += __shfl_down_sync(0xffffffffu, n_spill, off);
+        }
+        if (lane == 0) {
+            atomicAdd(&S.n_scan, n_scan);
+            atomicAdd(&S.n_spill, n_spill);
+            atomicAdd(&S.n_exp, n_exp);
+            atomicAdd(&S.n_dist, n_dist);
+        }
+        if (__any_sync(0xffffffffu, overflow) && lane == 0) atomicMax(&S.status, 2);
+        __syncthreads();
+
+        // ---------------------------------------------------------------- top-k out (src/search_gpu.cu:447-472, :716)
+        if (warp == 0) {
+            const int cnt = S.beam_cnt;
+            const float far0 = METRIC == 0 ? 3.402823466e+38f : -3.402823466e+38f;
+            int written = 0;
+            for (int base = 0; base < cnt && written < a.k; base += 32) {
+                const int i = base + lane;
+                bool ok = i < cnt;
+                uint64_t key = ok ? beam[i] : kPadKey;
+                const int id = key_id(key);
+                if (ok && a.deleted) ok = ((a.deleted[id >> 5] >> (id & 31)) & 1u) == 0u;
+                const uint32_t m = __ballot_sync(0xffffffffu, ok);
+                const int p = written + __popc(m & lt_mask);
+                if (ok && p < a.k) {
+                    a.ids_out[(size_t)qid * a.k + p] = id;
+                    if (a.dists_out) a.dists_out[(size_t)qid * a.k + p] = dist_of<METRIC>((uint32_t)(key >> 32));
+                }
+                written += __popc(m);
+            }
+            for (int p = written + lane; p < a.k; p += 32) {
+                a.ids_out[(size_t)qid * a.k + p] = -1;
+                if (a.dists_out) a.dists_out[(size_t)qid * a.k + p] = far0;
+            }
+            if (lane == 0) {
+                int st = S.status;
+                if (st == 0 && cnt < a.L) st = 1;
+                if (a.stats_out) {
+                    int32_t* o = a.stats_out + (size_t)qid * 8;
+                    o[0] = st;
+                    o[1] = S.n_dist;
+                    o[2] = S.n_exp;
+                    o[3] = S.rounds;
+                    o[4] = S.hops;
+                    o[5] = S.n_scan;
+                    o[6] = S.max_cand;
+                    o[7] = S.n_spill;
+                }
+                atomicAdd(a.hops_total, (unsigned long long)S.hops);
+            }
+        }
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_beam_search(const SearchArgs& a, int metric, int grid, cudaStream_t stream) {
+    const int threads = a.plan.warps * 32;
+    if (metric == 0)
+        beam_search_kernel<0><<<grid, threads, a.plan.smem_bytes, stream>>>(a);
+    else
+        beam_search_kernel<1><<<grid, threads, a.plan.smem_bytes, stream>>>(a);
+    return cudaGetLastError();
+}
+
+int beam_search_occupancy(const SearchPlan& p, int metric) {
+    const void* fn = metric == 0 ? (const void*)beam_search_kernel<0> : (const void*)beam_search_kernel<1>;
+    // The opt-in limit only ever grows: plans for other beam capacities stay launchable.
+    static int granted[2] = {0, 0};
+    if (p.smem_bytes > granted[metric]) {
+        if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes) != cudaSuccess) {
+            cudaGetLastError();
+            return 0;
+        }
+        granted[metric] = p.smem_bytes;
+    }
+    int nb = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, fn, p.warps * 32, p.smem_bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return nb;
+}
+
+}  // namespace coral

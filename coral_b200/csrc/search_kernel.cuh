@@ -1,0 +1,54 @@
+// Host/device shared declarations of the beam-search kernel (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace coral {
+
+// Shared-memory plan of one CTA, computed on the host for (dim, L, deg_pad) and
+// the tuning knobs; every offset is in bytes from the start of dynamic smem.
+struct SearchPlan {
+    int warps;        // warps per CTA; every warp runs its own gather/distance pipeline
+    int stages;       // per-warp ring depth (stages of 32 row chunks)
+    int chunk_bytes;  // bytes of one row chunk moved by one bulk copy (multiple of 16)
+    int n_chunks;     // chunks per row (chunk_bytes * n_chunks == dim * 4)
+    int row_stride;   // bytes between two rows inside a stage (padded against bank conflicts)
+    int stage_bytes;  // 32 * row_stride
+    int hs_bits;      // log2 entries of the shared-memory visited hash, 0 = none
+    int LP;           // beam array length: L rounded up to a power of two
+    int tile_max;     // largest candidate tile sorted at once (power of two)
+    int ctas_per_sm;
+    int off_query, off_beam0, off_beam1, off_exp, off_hash, off_bar, off_pend, off_bids, off_stage;
+    int smem_bytes;
+};
+
+struct SearchArgs {
+    const float* vecs;         // [n][dim]
+    const int32_t* adj;        // [n][deg_pad]
+    const float* queries;      // [Q][dim]
+    const int32_t* start_ids;  // [M]
+    const uint32_t* deleted;   // nullable bitset over n
+    int32_t* ids_out;          // [Q][k]
+    float* dists_out;          // nullable [Q][k]
+    int32_t* stats_out;        // nullable [Q][8]
+    unsigned long long* hops_total;  // sum of per-query hops
+    uint64_t* ghash;           // [grid][gh_mask+1] spill table of the visited set, epoch-tagged
+    uint64_t* gcand;           // [grid][cand_cap] candidates of the current round
+    int* q_counter;            // next query to take
+    int* err_flag;             // set when a bounded wait ran out
+    int64_t n;
+    int dim, deg_pad, deg_shift, M, Q, L, k;
+    uint32_t epoch_base;       // epoch of query q is epoch_base + q + 1 (never 0)
+    uint32_t gh_mask;
+    int cand_cap;              // L * deg_pad
+    int max_rounds;
+    SearchPlan plan;
+};
+
+// Launches the kernel for `metric` (0 = L2, 1 = IP) with `grid` CTAs on `stream`.
+cudaError_t launch_beam_search(const SearchArgs& a, int metric, int grid, cudaStream_t stream);
+// Registers the dynamic shared-memory size with the runtime and returns the
+// number of CTAs of this plan that fit one SM (0 on failure).
+int beam_search_occupancy(const SearchPlan& p, int metric);
+
+}  // namespace coral

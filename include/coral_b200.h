@@ -1,0 +1,160 @@
+/*
+ * coral_b200 -- C ABI of the B200 (sm_100a) batched graph beam search.
+ *
+ * Drop-in boundary for ONE path of the CORAL index: the batched "full expansion"
+ * beam search behind IndexGPU::Search.  Plain pointers and sizes only; every
+ * function returns a status code (0 = CORAL_OK), never exits the process and
+ * never traps the device.  Each declaration cites the reference interface it
+ * replaces (paths are relative to the reference project).
+ *
+ * Layout in device memory (owned by the handle unless attached):
+ *   vectors    float  [n][dim]       row-major, rows are dim*4 bytes, dim % 4 == 0
+ *   adjacency  int32  [n][deg_pad]   deg_pad = max_degree rounded up to 32/64/128,
+ *                                    valid neighbour ids first, -1 padding
+ *   start ids  int32  [M]
+ * Distances follow the reference: L2 is the squared distance (no sqrt), IP is
+ * the raw dot product and LARGER means closer (include/utils.cuh:254-323,380-382).
+ */
+#ifndef CORAL_B200_H
+#define CORAL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* DIST_METRIC (include/uni.h) */
+#define CORAL_L2 0
+#define CORAL_IP 1
+
+/* status codes */
+#define CORAL_OK 0
+#define CORAL_ERR_ARG 1      /* bad argument (null pointer, size out of range, dim % 4 != 0 ...) */
+#define CORAL_ERR_STATE 2    /* call order: vectors/adjacency/start ids/prepare missing */
+#define CORAL_ERR_CUDA 3     /* a CUDA runtime call failed; see coral_last_error */
+#define CORAL_ERR_NOGPU 4    /* no usable CUDA device: there is no CPU fallback */
+#define CORAL_ERR_KERNEL 5   /* the kernel gave up on a bounded wait; results are invalid */
+#define CORAL_ERR_LIMIT 6    /* request exceeds what coral_search_prepare sized */
+
+/* per-query status written to stats[q][0] */
+#define CORAL_Q_OK 0
+#define CORAL_Q_BEAM_UNDERFULL 1  /* fewer than L nodes reachable (reference asserts, src/search_gpu.cu:444) */
+#define CORAL_Q_HASH_OVERFLOW 2   /* visited set outgrew its tables: result approximate */
+#define CORAL_Q_ROUND_LIMIT 3     /* stopped by the round bound */
+
+/* stats row per query: status, n_dist, n_exp, rounds, hops, n_scan, max_cand, n_spill */
+#define CORAL_STATS_W 8
+
+typedef struct coral_index coral_index_t;
+
+/* Library version and the SM architecture the kernels were compiled for (100). */
+int coral_version(void);
+int coral_compiled_sm(void);
+
+/* Replaces the GPU branch of Graph::Graph (include/graph.cuh:222-266) and
+ * GPUFuncs::GPUFuncs (src/gpufuncs.cu:70-118): binds a handle to `device`
+ * and records the index geometry.  metric: CORAL_L2 | CORAL_IP. */
+int coral_index_create(coral_index_t** out, int device, int64_t n, int dim, int max_degree, int metric);
+
+/* Replaces RunFree / ~Graph: releases every device allocation of the handle. */
+int coral_index_destroy(coral_index_t* h);
+
+/* Replaces the base-vector cudaMemcpy at include/graph.cuh:260-261.  `vecs`
+ * may be a host or a device pointer to n*dim floats; the data is copied. */
+int coral_index_set_vectors(coral_index_t* h, const float* vecs);
+
+/* Same, without the copy: `dev_vecs` must stay valid (and 16-byte aligned)
+ * for the life of the handle.  No counterpart in the reference. */
+int coral_index_attach_vectors(coral_index_t* h, const float* dev_vecs);
+
+/* Replaces the Slot upload at include/graph.cuh:258-259.  Takes the graph as
+ * the reference's Slot array presents it (include/disk_graph.h:30-35): for node
+ * i, degs[i*deg_stride] neighbours at nbrs[i*nbr_stride + 0..deg).  Strides are
+ * in int32 units (a Slot array is deg_stride = nbr_stride = 100).  Host
+ * pointers.  Degrees above max_degree are cut (src/graph.cu:723-727). */
+int coral_index_set_slots(coral_index_t* h, const int32_t* degs, size_t deg_stride,
+                          const int32_t* nbrs, size_t nbr_stride);
+
+/* The same graph already in the padded device layout: int32 [n][deg_pad], -1
+ * padding.  Host or device pointer; copied. */
+int coral_index_set_adjacency(coral_index_t* h, const int32_t* adj, int deg_pad);
+
+/* Replaces Graph::load_search_start_nodes / get_start_ids
+ * (src/graph.cpp:329-351): all M ids are used as entry points, duplicates kept
+ * (src/search_gpu.cu:392-407). */
+int coral_index_set_start_ids(coral_index_t* h, const int32_t* ids, int M);
+
+/* Replaces d_deleted (src/search_gpu.cu:582-833, :716): bit i set = node i is
+ * skipped when the final top-k is written.  Host pointer to (n+31)/32 words, or
+ * NULL to clear. */
+int coral_index_set_deleted(coral_index_t* h, const uint32_t* bits);
+
+/* Replaces GPUFuncs::search_prepare (src/search.cu:400-440): sizes every
+ * scratch buffer once for up to max_queries per call, beam capacity <= max_L
+ * and k <= max_k.  The reference reallocates on every Search. */
+int coral_search_prepare(coral_index_t* h, int max_queries, int max_L, int max_k);
+
+/* Replaces GPUFuncs::search_free (src/search.cu:442-456). */
+int coral_search_free(coral_index_t* h);
+
+/* Replaces IndexGPU::Search (src/index_gpu.cpp:117-136) + GPUFuncs::search_gpu
+ * (src/search_gpu.cu:835-886).  queries: Q*dim floats, ids_out: Q*k int32,
+ * dists_out (may be NULL): Q*k floats, stats_out (may be NULL): Q*CORAL_STATS_W
+ * int32 -- each a HOST or a DEVICE pointer (detected).  L = beam capacity,
+ * k <= L, M = number of start ids <= L.  Blocks until results are in place.
+ * total_hops_out (may be NULL) receives the reference's Test_Result::hops. */
+int coral_search(coral_index_t* h, const float* queries, int Q, int L, int k, int32_t* ids_out,
+                 float* dists_out, int32_t* stats_out, int64_t* total_hops_out);
+
+/* The kernel window alone: all pointers are device pointers, the launch is
+ * enqueued on `stream` (a cudaStream_t, NULL = the handle's stream) and the
+ * call returns without synchronising.  Check coral_search_check afterwards. */
+int coral_search_async(coral_index_t* h, const float* d_queries, int Q, int L, int k,
+                       int32_t* d_ids_out, float* d_dists_out, int32_t* d_stats_out, void* stream);
+
+/* After the stream has been synchronised: CORAL_ERR_KERNEL if the last launch
+ * reported a bounded wait that ran out, else CORAL_OK. */
+int coral_search_check(coral_index_t* h);
+
+/* Device time in milliseconds of the last coral_search's kernel window (the
+ * reference's timed window, src/search_gpu.cu:861-877) and of the whole call. */
+float coral_last_kernel_ms(coral_index_t* h);
+float coral_last_total_ms(coral_index_t* h);
+
+/* Number of kernels this library launched on behalf of the handle so far. */
+int64_t coral_launch_count(coral_index_t* h);
+
+/* Tuning knobs (before coral_search_prepare): "ctas_per_sm", "warps",
+ * "chunk_bytes", "stages", "smem_hash_bits" (0 = visited set entirely in the
+ * global table), "ghash_factor", "ghash_entries", "max_rounds".  Returns CORAL_ERR_ARG for
+ * unknown names. */
+int coral_set_option(coral_index_t* h, const char* name, int value);
+int coral_get_option(coral_index_t* h, const char* name, int* value);
+
+/* Replaces ids_verify_kernel / GPUFuncs::search_verify
+ * (src/search_gpu.cu:888-922): hits = sum_q |res[q][0..k) ∩ gt[q][0..k)|, gt rows
+ * are gt_dim wide (tests/test_search_pipeline.cpp:25-39).  Host or device
+ * pointers. */
+int coral_count_hits(coral_index_t* h, const int32_t* res, const int32_t* gt, int Q, int k,
+                     int gt_dim, int64_t* hits_out);
+
+/* Shard merge (no counterpart in the reference, which is single-GPU): ids and
+ * dists hold G per-shard results [G][Q][k] (global ids, -1 = padding); writes
+ * the k closest per query by (distance, id).  Device pointers; enqueued on
+ * `stream` without synchronising. */
+int coral_merge_shards(coral_index_t* h, const int32_t* d_ids, const float* d_dists, int G, int Q,
+                       int k, int32_t* d_ids_out, float* d_dists_out, void* stream);
+
+/* Maps shard-local result ids to global ids in place through id_map[n_local]
+ * (device pointers; ids < 0 stay).  No counterpart in the reference. */
+int coral_map_ids(coral_index_t* h, int32_t* d_ids, int64_t count, const int32_t* d_id_map, void* stream);
+
+/* Last error text of the handle (or of handle creation when h is NULL). */
+const char* coral_last_error(coral_index_t* h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CORAL_B200_H */
