@@ -23,11 +23,14 @@ namespace {
 thread_local std::string g_create_error;
 
 struct Options {
-    int ctas_per_sm = 2;
+    // Defaults from a sweep on 10M x 512 (one B200): many small CTAs beat few large ones, one
+    // 256-byte stage per warp beats deeper rings, and shared memory spent on more resident
+    // CTAs beats spending it on a shared-memory visited table.
+    int ctas_per_sm = 0;  // 0 = as many as shared memory allows (at most 8)
     int warps = 4;
     int chunk_bytes = 256;
-    int stages = 0;  // 0 = as many as fit (at most 6)
-    int smem_hash_bits = 12;
+    int stages = 0;  // 0 = one stage when ctas_per_sm is automatic, else as many as fit (at most 6)
+    int smem_hash_bits = 0;
     int ghash_factor = 8;  // global visited table entries >= factor * L * deg_pad
     int ghash_entries = 0; // explicit table size (power of two >= 64), 0 = from ghash_factor
     int max_rounds = 1 << 16;
@@ -116,7 +119,8 @@ bool make_plan(const coral_index* h, int L, SearchPlan& p, std::string& why) {
     const int row_bytes = h->dim * 4;
     p = SearchPlan{};
     p.warps = std::min(std::max(o.warps, 1), 16);
-    p.ctas_per_sm = std::min(std::max(o.ctas_per_sm, 1), 8);
+    const bool auto_ctas = o.ctas_per_sm <= 0;
+    p.ctas_per_sm = auto_ctas ? 1 : std::min(o.ctas_per_sm, 8);
     int target = std::max(16, o.chunk_bytes);
     int nc = (row_bytes + target - 1) / target;
     while (nc <= row_bytes / 16 && !(row_bytes % nc == 0 && (row_bytes / nc) % 16 == 0)) ++nc;
@@ -147,8 +151,9 @@ bool make_plan(const coral_index* h, int L, SearchPlan& p, std::string& why) {
         const int room = budget - off;
         int st = room / (p.warps * p.stage_bytes);
         if (o.stages > 0) st = std::min(st, o.stages);
+        else if (auto_ctas) st = std::min(st, 1);
         st = std::min(st, 6);
-        if (st >= 1 && (st >= 2 || p.hs_bits == 0)) {
+        if (st >= 1) {
             p.stages = st;
             p.smem_bytes = off + p.warps * st * p.stage_bytes;
             break;
@@ -157,14 +162,10 @@ bool make_plan(const coral_index* h, int L, SearchPlan& p, std::string& why) {
             p.hs_bits = p.hs_bits > 8 ? p.hs_bits - 1 : 0;
             continue;
         }
-        if (st >= 1) {
-            p.stages = st;
-            p.smem_bytes = off + p.warps * st * p.stage_bytes;
-            break;
-        }
         why = "shared memory budget too small for this dim/L/warps/ctas_per_sm";
         return false;
     }
+    if (auto_ctas) p.ctas_per_sm = std::min(std::max(h->smem_optin / (p.smem_bytes + 1024), 1), 8);
     int tile = 64;
     const int cap = std::min(p.warps * p.stages * p.stage_bytes / 8, 2048);
     while (tile * 2 <= cap) tile <<= 1;
@@ -519,7 +520,7 @@ int coral_search_prepare(coral_index_t* h, int max_queries, int max_L, int max_k
     int per_sm = 0;
     if (int rc = get_plan(h, max_L, p, per_sm)) return rc;
     // smaller L never needs more CTAs than ctas_per_sm allows
-    h->grid_cap = h->sm_count * std::max(per_sm, h->opt.ctas_per_sm);
+    h->grid_cap = h->sm_count * (h->opt.ctas_per_sm <= 0 ? 8 : std::max(per_sm, h->opt.ctas_per_sm));
     h->max_q = max_queries;
     h->max_L = max_L;
     h->max_k = max_k;

@@ -75,14 +75,16 @@ def make_l2_mixture(n: int, n_train: int, n_test: int, dim: int = 200, centers: 
 
 
 def make_ip_cones(n: int, n_train: int, n_test: int, dim: int = 512, clusters: int = 1,
-                  cos_uv: float = 0.3, sigma: float = 0.15, spread: float = 1.0,
+                  cos_uv: float = 0.3, sigma: float = 0.15, spread: float = 1.0, latent_dim: int = 16,
                   seed: int = 20260001, device="cpu", chunk: int = 1 << 20) -> Dataset:
     """CLIP-like inner-product case: unit vectors.  Base points scatter around a mean
     direction u, queries around v with cos(u, v) = `cos_uv` (the modality gap).
     With `clusters` > 1 each base cluster j has its own direction normalise(u + spread*g_j)
     and a query aimed at cluster j is normalise(v + spread*g_j + noise): the two modalities
-    share the cluster offsets g_j but not the mean direction.  Per-point noise is isotropic
-    with per-coordinate deviation sigma/sqrt(dim) (total deviation `sigma`)."""
+    share the cluster offsets g_j but not the mean direction.  The offsets live in a random
+    `latent_dim`-dimensional subspace (0 = the full space), so that clusters have near and
+    far neighbours the way real embedding sets do.  Per-point noise is isotropic with
+    per-coordinate deviation sigma/sqrt(dim) (total deviation `sigma`)."""
     g = _gen(seed, device)
     u = torch.randn(dim, generator=g, device=device)
     u /= u.norm()
@@ -90,7 +92,10 @@ def make_ip_cones(n: int, n_train: int, n_test: int, dim: int = 512, clusters: i
     w -= (w @ u) * u
     w /= w.norm()
     v = cos_uv * u + math.sqrt(1.0 - cos_uv * cos_uv) * w
-    if clusters > 1:
+    if clusters > 1 and latent_dim > 0:
+        basis, _ = torch.linalg.qr(torch.randn(dim, latent_dim, generator=g, device=device))
+        gj = (torch.randn(clusters, latent_dim, generator=g, device=device) @ basis.T) * (spread / math.sqrt(latent_dim))
+    elif clusters > 1:
         gj = torch.randn(clusters, dim, generator=g, device=device) * (spread / math.sqrt(dim))
     else:
         gj = torch.zeros(1, dim, device=device)
@@ -175,7 +180,7 @@ def _pad_degree(max_degree: int) -> int:
 @torch.no_grad()
 def _coarse_assign(base: torch.Tensor, n_cells: int, metric: str, seed: int, iters: int = 2,
                    chunk: int = 1 << 18):
-    """A few Lloyd iterations from sampled centroids; returns cell id per base row."""
+    """A few Lloyd iterations from sampled centroids; returns (cell id per base row, centroids)."""
     n = base.shape[0]
     g = _gen(seed, base.device)
     cent = base[torch.randperm(n, generator=g, device=base.device)[:n_cells]].clone()
@@ -189,7 +194,7 @@ def _coarse_assign(base: torch.Tensor, n_cells: int, metric: str, seed: int, ite
         sums = torch.zeros_like(cent).index_add_(0, assign, base)
         cnt = torch.bincount(assign, minlength=n_cells).clamp_(min=1).to(base.dtype)
         cent = sums / cnt[:, None]
-    return assign
+    return assign, cent
 
 
 @torch.no_grad()
@@ -226,7 +231,8 @@ def _cell_knn(base: torch.Tensor, assign: torch.Tensor, n_cells: int, kk: int, m
 def build_graph(base: torch.Tensor, train: torch.Tensor, metric: str, max_degree: int = 32,
                 k_b: int = 100, n_start: int = 16, seed: int = 20260004,
                 train_knn: torch.Tensor | None = None, nap_per_node: int = 12,
-                cell_size: int = 2048, list_batch: int = 2048, routers: bool = True) -> Graph:
+                cell_size: int = 2048, list_batch: int = 2048, routers: bool = True,
+                long_links: int = 4) -> Graph:
     """Fixed-degree directed graph in the reference's spirit.
 
     1. k_b-NN list of every training query (exact unless `train_knn` is given).
@@ -252,7 +258,9 @@ def build_graph(base: torch.Tensor, train: torch.Tensor, metric: str, max_degree
         kb = train_knn.shape[1]
         m = min(nap_per_node, kb - 1)
 
+        # ---- projection edges, grouped per node: nap[N, R], closest first
         src_l, dst_l, d_l = [], [], []
+        eye = torch.eye(kb, dtype=torch.bool, device=dev)[None]
         for s in range(0, train_knn.shape[0], list_batch):
             ids = train_knn[s:s + list_batch].long()              # [B, kb]
             x = base[ids]                                         # [B, kb, dim]
@@ -260,54 +268,111 @@ def build_graph(base: torch.Tensor, train: torch.Tensor, metric: str, max_degree
             if metric == L2:
                 sq = x.pow(2).sum(2)
                 sc = 2.0 * sc - sq[:, None, :] - sq[:, :, None]    # -|a-b|^2
-            eye = torch.eye(kb, dtype=torch.bool, device=dev)[None]
             sc = sc.masked_fill(eye, -float("inf"))
             ts, ti = torch.topk(sc, m, dim=2)                     # [B, kb, m]
-            u = ids[:, :, None].expand(-1, -1, m)
-            v = ids.gather(1, ti.reshape(ids.shape[0], -1)).reshape(ids.shape[0], kb, m)
-            src_l += [u.reshape(-1), v.reshape(-1)]               # forward and reverse proposals
-            dst_l += [v.reshape(-1), u.reshape(-1)]
+            u = ids[:, :, None].expand(-1, -1, m).reshape(-1).to(torch.int32)
+            v = ids.gather(1, ti.reshape(ids.shape[0], -1)).reshape(-1).to(torch.int32)
+            src_l += [u, v]                                       # forward and reverse proposals
+            dst_l += [v, u]
             d_l += [-ts.reshape(-1), -ts.reshape(-1)]
-        src = torch.cat(src_l)
-        dst = torch.cat(dst_l)
+            del x, sc, ts, ti
+        key = torch.cat(src_l).long() * n + torch.cat(dst_l).long()
         dd = torch.cat(d_l)
         del src_l, dst_l, d_l
-
-        n_cells = max(1, n // cell_size)
-        assign = _coarse_assign(base, n_cells, metric, seed)
-        cell_nb = _cell_knn(base, assign, n_cells, max_degree, metric)  # [N, R]
-        cu = torch.arange(n, device=dev)[:, None].expand(-1, cell_nb.shape[1]).reshape(-1)
-        cv = cell_nb.reshape(-1).long()
-        keep = cv >= 0
-        cu, cv = cu[keep], cv[keep]
-        # rank inside the cell list is already closest first: use it as the distance key
-        cr = torch.arange(cell_nb.shape[1], device=dev, dtype=torch.float32)[None, :].expand(n, -1).reshape(-1)[keep]
-
-        # group key: (node, class, distance); class 0 = projection edge, 1 = cell edge
-        all_u = torch.cat([src, cu])
-        all_v = torch.cat([dst, cv])
-        all_c = torch.cat([torch.zeros_like(src), torch.ones_like(cu)])
-        all_d = torch.cat([dd, cr])
-        del src, dst, dd, cu, cv, cr
-        # dedupe (u, v): keep the first occurrence in (u, v, class) order
-        o = torch.argsort(all_c, stable=True)
-        all_u, all_v, all_c, all_d = all_u[o], all_v[o], all_c[o], all_d[o]
-        o = torch.argsort(all_u * n + all_v, stable=True)
-        all_u, all_v, all_c, all_d = all_u[o], all_v[o], all_c[o], all_d[o]
-        first = torch.ones_like(all_u, dtype=torch.bool)
-        first[1:] = (all_u[1:] != all_u[:-1]) | (all_v[1:] != all_v[:-1])
-        all_u, all_v, all_c, all_d = all_u[first], all_v[first], all_c[first], all_d[first]
-        # order inside a node: class, then distance
-        o = torch.argsort(all_d, stable=True)
-        all_u, all_v, all_c = all_u[o], all_v[o], all_c[o]
-        o = torch.argsort(all_u * 2 + all_c, stable=True)
-        all_u, all_v = all_u[o], all_v[o]
+        o = torch.argsort(dd, stable=True)                        # smallest distance first ...
+        key = key[o]
+        del o, dd
+        key = key[torch.argsort(key, stable=True)]                # ... inside every (u, v) group
+        first = torch.ones_like(key, dtype=torch.bool)
+        first[1:] = key[1:] != key[:-1]
+        # one entry per (u, v) now; rank them per node by distance again: the distance order
+        # was lost by the key sort, so recompute it for the survivors.
+        key = key[first]
+        del first
+        uu, vv = key // n, key % n
+        del key
+        dd = torch.empty(uu.shape[0], device=dev)
+        for s in range(0, uu.shape[0], 1 << 22):
+            a_, b_ = base[uu[s:s + (1 << 22)]], base[vv[s:s + (1 << 22)]]
+            dd[s:s + (1 << 22)] = ((a_ - b_).pow(2).sum(1) if metric == L2 else -(a_ * b_).sum(1))
+            del a_, b_
+        o = torch.argsort(dd, stable=True)
+        uu, vv = uu[o], vv[o]
+        del o, dd
+        o = torch.argsort(uu, stable=True)
+        uu, vv = uu[o], vv[o]
+        del o
         start = torch.zeros(n + 1, dtype=torch.int64, device=dev)
-        start[1:] = torch.cumsum(torch.bincount(all_u, minlength=n), 0)
-        rank = torch.arange(all_u.shape[0], device=dev) - start[all_u]
+        start[1:] = torch.cumsum(torch.bincount(uu, minlength=n), 0)
+        rank = torch.arange(uu.shape[0], device=dev) - start[uu]
         keep = rank < max_degree
+        nap = torch.full((n, max_degree), -1, dtype=torch.int32, device=dev)
+        nap[uu[keep], rank[keep]] = vv[keep].to(torch.int32)
+        del uu, vv, rank, keep, start
+
+        # ---- base-space neighbours inside the coarse cell: cell_nb[N, R], closest first
+        n_cells = max(1, n // cell_size)
+        assign, cent = _coarse_assign(base, n_cells, metric, seed)
+        cell_nb = _cell_knn(base, assign, n_cells, max_degree, metric)
+
+        # ---- links between cells.  The representative of a cell is its member that appears in
+        # the most training lists (closest to the centroid among equals); every node gets
+        # `long_links` edges to representatives of cells near its own, and a representative
+        # links to all of them, so that a search can walk from cell to cell.
+        n_near = min(n_cells - 1, 16)
+        if n_near > 0 and long_links > 0:
+            pop = torch.bincount(train_knn.reshape(-1).long(), minlength=n).to(torch.float32)
+            closeness = torch.empty(n, device=dev)
+            for s in range(0, n, 1 << 20):
+                closeness[s:s + (1 << 20)] = -(base[s:s + (1 << 20)] - cent[assign[s:s + (1 << 20)]]).pow(2).sum(1)
+            o = torch.argsort(closeness, descending=True, stable=True)
+            o = o[torch.argsort(pop[o], descending=True, stable=True)]
+            o = o[torch.argsort(assign[o], stable=True)]             # per cell: most popular, then most central
+            cell_of = assign[o]
+            head = torch.ones_like(cell_of, dtype=torch.bool)
+            head[1:] = cell_of[1:] != cell_of[:-1]
+            rep = torch.full((n_cells,), -1, dtype=torch.int64, device=dev)
+            rep[cell_of[head]] = o[head]
+            live = rep >= 0
+            cc = cent.clone()
+            cc[~live] = float("inf")                                  # empty cells are nobody's neighbour
+            dcell = torch.cdist(cent, cc)
+            dcell.fill_diagonal_(float("inf"))
+            near = torch.topk(dcell, n_near, dim=1, largest=False).indices      # [cells, n_near]
+            near_rep = rep[near]                                                  # [cells, n_near]
+            ll = min(long_links, n_near)
+            pick = (torch.arange(n, device=dev)[:, None] * 7 + torch.arange(ll, device=dev)[None, :] * (n_near // ll)) % n_near
+            longs = near_rep[assign[:, None].expand(-1, ll), pick].to(torch.int32)        # [N, ll]
+            rep_rows = near_rep[live].to(torch.int32)                                     # [live cells, n_near]
+            rep_ids = rep[live]
+        else:
+            longs = torch.full((n, 0), -1, dtype=torch.int32, device=dev)
+            rep_rows = rep_ids = None
+        del assign
+
+        # ---- per node: links to other cells, projection edges, then cell edges; duplicates
+        # of an earlier entry are dropped and the row cut to max_degree
         adj = torch.full((n, deg_pad), -1, dtype=torch.int32, device=dev)
-        adj[all_u[keep], rank[keep]] = all_v[keep].to(torch.int32)
+
+        def pack_rows(parts):
+            x = torch.cat(parts, 1)
+            w = x.shape[1]
+            eq = x[:, :, None] == x[:, None, :]
+            eq &= torch.tril(torch.ones(w, w, dtype=torch.bool, device=dev), diagonal=-1)[None]
+            x = torch.where(eq.any(2), torch.full_like(x, -1), x)
+            o_ = torch.argsort((x < 0).to(torch.int8), dim=1, stable=True)
+            return x.gather(1, o_)[:, :max_degree]
+
+        width = longs.shape[1] + 2 * max_degree
+        row_chunk = max(1, (1 << 27) // (width * width))
+        for s in range(0, n, row_chunk):
+            adj[s:s + row_chunk, :max_degree] = pack_rows(
+                [longs[s:s + row_chunk], nap[s:s + row_chunk], cell_nb[s:s + row_chunk]])
+        if rep_ids is not None:
+            for s in range(0, rep_ids.shape[0], row_chunk):
+                r_ = rep_ids[s:s + row_chunk]
+                adj[r_, :max_degree] = pack_rows([rep_rows[s:s + row_chunk], nap[r_], cell_nb[r_]])
+        del nap, cell_nb, longs
 
         # entry points and routers: k-means of the training queries; the base point closest
         # to each of `n_start` coarse centroids is an entry point, and the row of entry point
@@ -324,18 +389,25 @@ def build_graph(base: torch.Tensor, train: torch.Tensor, metric: str, max_degree
                 cent = sums / cnt[:, None]
             if metric == IP:
                 cent = _normalize_(cent)
-            return exact_knn(base, cent, 1, metric)[:, 0].long()
+            return exact_knn(base, cent, 1, metric)[:, 0].long(), cent
 
-        start_ids = torch.unique(kmeans_nearest(4 * n_start, seed + 1))[:n_start]
+        start_ids = torch.unique(kmeans_nearest(4 * n_start, seed + 1)[0])[:n_start]
         if routers and n > 4 * n_start * max_degree:
-            rt = torch.unique(kmeans_nearest(n_start * max_degree, seed + 2))
+            rt, rcent = kmeans_nearest(n_start * max_degree, seed + 2)
+            # a router first points at the representatives of the cells closest (query-to-base
+            # metric) to its query centroid, then keeps what is left of its own row
+            if rep_ids is not None:
+                n_rep = min(max_degree // 2, rep_ids.shape[0])
+                rep_links = rep_ids[torch.topk(_scores(rcent, base[rep_ids], metric), n_rep, dim=1).indices]
+                for s in range(0, rt.shape[0], row_chunk):
+                    r_ = rt[s:s + row_chunk]
+                    adj[r_, :max_degree] = pack_rows([rep_links[s:s + row_chunk].to(torch.int32), adj[r_, :max_degree]])
+            rt = torch.unique(rt)
             rt = rt[~torch.isin(rt, start_ids)]
             rows = torch.full((start_ids.shape[0] * max_degree,), -1, dtype=torch.int32, device=dev)
             rows[:rt.shape[0]] = rt.to(torch.int32)[:rows.shape[0]]
-            rows = rows.reshape(start_ids.shape[0], max_degree).T.contiguous().T  # keep row-major
-            # valid ids first inside every row
-            o = torch.argsort((rows < 0).to(torch.int8), dim=1, stable=True)
-            adj[start_ids, :max_degree] = rows.gather(1, o)
+            rows = rows.reshape(start_ids.shape[0], max_degree)
+            adj[start_ids, :max_degree] = rows          # valid ids first: unused slots trail
             adj[start_ids, max_degree:] = -1
         return Graph(adj.contiguous(), start_ids.to(torch.int32), max_degree)
     finally:
