@@ -25,7 +25,7 @@ EXPORTS = (
     "coral_search_prepare", "coral_search_free", "coral_search", "coral_search_async",
     "coral_search_check", "coral_last_kernel_ms", "coral_last_total_ms", "coral_launch_count",
     "coral_set_option", "coral_get_option", "coral_count_hits", "coral_merge_shards",
-    "coral_map_ids", "coral_last_error",
+    "coral_map_ids", "coral_last_error", "coral_search_static",
 )
 
 _lib = None
@@ -74,6 +74,8 @@ def load():
         "coral_merge_shards": (C.c_int, [vp, i32p, f32p, C.c_int, C.c_int, C.c_int, i32p, f32p, vp]),
         "coral_map_ids": (C.c_int, [vp, i32p, C.c_int64, i32p, vp]),
         "coral_last_error": (C.c_char_p, [vp]),
+        "coral_search_static": (C.c_int, [C.c_int, vp, f32p, i32p, C.c_int64, C.c_int, C.c_int, C.c_int, i32p, C.c_int,
+                                          f32p, C.c_int, C.c_int, C.c_int, i32p, f32p]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

@@ -151,6 +151,24 @@ int coral_merge_shards(coral_index_t* h, const int32_t* d_ids, const float* d_di
  * (device pointers; ids < 0 stay).  No counterpart in the reference. */
 int coral_map_ids(coral_index_t* h, int32_t* d_ids, int64_t count, const int32_t* d_id_map, void* stream);
 
+/* The beam search for callers that cannot allocate device memory at search time
+ * (a server whose pool already owns the GPU, a plugin inside another framework's
+ * callback, code under an allocation guard).  It has no counterpart in the
+ * reference, whose Search allocates on every call (src/index_gpu.cpp:117-136).
+ * Same kernel and same results as coral_search, but the kernel's scratch (visited
+ * table, candidate buffers) lives in a 64 MiB array inside the library image, so
+ * this function calls no cudaMalloc/cudaFree and builds no host containers.
+ * Every pointer is a device pointer owned by the caller; adjacency is the padded
+ * layout [n][deg_pad].  Limits: L * deg_pad <= 16384 (CORAL_ERR_LIMIT beyond),
+ * Q <= 2^24.  The first call on a device resolves the array's address: make it
+ * before any stream capture.  All calls share the array, which keeps the last
+ * call's contents (control words are re-zeroed, table entries are epoch-tagged);
+ * calls that overlap on one GPU race.  Runs on `stream` and returns after
+ * synchronising it. */
+int coral_search_static(int device, void* stream, const float* d_vecs, const int32_t* d_adj, int64_t n,
+                        int dim, int deg_pad, int metric, const int32_t* d_start_ids, int M,
+                        const float* d_queries, int Q, int L, int k, int32_t* d_ids_out, float* d_dists_out);
+
 /* Last error text of the handle (or of handle creation when h is NULL). */
 const char* coral_last_error(coral_index_t* h);
 
