@@ -49,17 +49,22 @@ class Dataset:
 
 def make_l2_mixture(n: int, n_train: int, n_test: int, dim: int = 200, centers: int = 1000,
                     sigma: float = 0.3, rot_dims: int = 60, offset: float = 0.5,
-                    seed: int = 20260001, device="cpu", chunk: int = 1 << 20) -> Dataset:
+                    seed: int = 20260001, device="cpu", chunk: int = 1 << 20,
+                    draw_seed: int | None = None) -> Dataset:
     """Text-to-image-like L2 case: a Gaussian mixture for the base; queries are the same
     mixture pushed through a fixed random rotation of a `rot_dims` subspace plus a fixed
-    mean offset (the modality gap)."""
+    mean offset (the modality gap).  `seed` fixes the mixture and the queries; `draw_seed`
+    (default: derived from seed) fixes the base points, so shards of one index can be drawn
+    independently with the same structure and the same queries."""
     g = _gen(seed, device)
+    gens = {False: _gen(seed + 1 if draw_seed is None else draw_seed, device), True: _gen(seed + 2, device)}
     ctr = torch.randn(centers, dim, generator=g, device=device)
     qr, _ = torch.linalg.qr(torch.randn(rot_dims, rot_dims, generator=g, device=device))
     off = offset * torch.randn(dim, generator=g, device=device)
 
     def draw(m, as_query):
         out = torch.empty(m, dim, device=device)
+        g = gens[as_query]
         for s in range(0, m, chunk):
             e = min(m, s + chunk)
             c = torch.randint(0, centers, (e - s,), generator=g, device=device)
@@ -76,7 +81,8 @@ def make_l2_mixture(n: int, n_train: int, n_test: int, dim: int = 200, centers: 
 
 def make_ip_cones(n: int, n_train: int, n_test: int, dim: int = 512, clusters: int = 1,
                   cos_uv: float = 0.3, sigma: float = 0.15, spread: float = 1.0, latent_dim: int = 16,
-                  seed: int = 20260001, device="cpu", chunk: int = 1 << 20) -> Dataset:
+                  seed: int = 20260001, device="cpu", chunk: int = 1 << 20,
+                  draw_seed: int | None = None) -> Dataset:
     """CLIP-like inner-product case: unit vectors.  Base points scatter around a mean
     direction u, queries around v with cos(u, v) = `cos_uv` (the modality gap).
     With `clusters` > 1 each base cluster j has its own direction normalise(u + spread*g_j)
@@ -100,8 +106,10 @@ def make_ip_cones(n: int, n_train: int, n_test: int, dim: int = 512, clusters: i
     else:
         gj = torch.zeros(1, dim, device=device)
     s = sigma / math.sqrt(dim)
+    g_base = _gen(seed + 1 if draw_seed is None else draw_seed, device)
+    g_query = _gen(seed + 2, device)
 
-    def draw(m, mean):
+    def draw(m, mean, g):
         out = torch.empty(m, dim, device=device)
         for a in range(0, m, chunk):
             e = min(m, a + chunk)
@@ -110,7 +118,8 @@ def make_ip_cones(n: int, n_train: int, n_test: int, dim: int = 512, clusters: i
             out[a:e] = _normalize_(x)
         return out
 
-    return Dataset(draw(n, u), draw(n_train, v), draw(n_test, v), IP, f"ip_cones_{n}x{dim}_c{clusters}")
+    return Dataset(draw(n, u, g_base), draw(n_train, v, g_query), draw(n_test, v, g_query), IP,
+                   f"ip_cones_{n}x{dim}_c{clusters}")
 
 
 # ----------------------------------------------------------------------------------------------

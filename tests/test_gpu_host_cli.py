@@ -1,0 +1,73 @@
+"""End to end through the C++ mirror: files in the reference's formats -> efanna2e::IndexGPU
+(LoadSearchNeededData, RunPrepare, Search) driven by the test_search_pipeline binary with the
+reference's flags -> ids identical to the CPU oracle's."""
+import os
+import struct
+import subprocess
+
+import numpy as np
+import pytest
+
+from coral_b200.host import build_host
+from oracle import oracle
+from tests import cases
+from tests.test_host_formats import _literal_block, write_reference_graph_dir
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("metric", ["l2", "ip"])
+def test_search_pipeline_driver_matches_oracle(tmp_path, metric):
+    import torch
+    from coral_b200 import synth
+    build_host.build()
+    c = cases.structured(metric)
+    k = 10
+    # for inner product hand the driver un-normalised copies: it must normalise base and queries itself
+    scale = np.linspace(0.5, 2.0, c.n, dtype=np.float32)[:, None] if metric == "ip" else 1.0
+    qscale = np.float32(3.0) if metric == "ip" else np.float32(1.0)
+    (tmp_path / "base.fbin").write_bytes(struct.pack("<ii", c.n, c.dim) + (c.base * scale).astype(np.float32).tobytes())
+    (tmp_path / "query.fbin").write_bytes(struct.pack("<ii", len(c.queries), c.dim) + (c.queries * qscale).tobytes())
+    gt = synth.exact_knn(torch.from_numpy(c.base), torch.from_numpy(c.queries), 100, metric).numpy()
+    (tmp_path / "gt.bin").write_bytes(struct.pack("<ii", gt.shape[0], gt.shape[1]) + gt.astype(np.int32).tobytes())
+    degs = (c.adj >= 0).sum(1)
+    write_reference_graph_dir(str(tmp_path / "graph"), degs, c.adj, _literal_block)
+    (tmp_path / "graph" / "graph.search_start_ids").write_text(
+        f"{len(c.start)} " + " ".join(str(int(v)) for v in c.start) + " ")
+    (tmp_path / "config.json").write_text('{"dim": %d, "k": 100, "search_start_nodes_num": 16}' % c.dim)
+    exe = os.path.join(os.path.dirname(build_host.HOST_LIB), "test_search_pipeline")
+    cmd = [exe, "--dataset", "synthetic", "--data_type", "float", "--dist", metric,
+           "--base_data_path", str(tmp_path / "base.fbin"), "--query_path", str(tmp_path / "query.fbin"),
+           "--gt_path", str(tmp_path / "gt.bin"), "--graph_path", str(tmp_path / "graph"),
+           "--config_file", str(tmp_path / "config.json"), "--max_degree", "32", "--k", str(k),
+           "--L", "64", "128", "-T", "8", "--csv", str(tmp_path / "out.csv"), "--ids_out", str(tmp_path / "ids.bin")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    rows = [ln.split(",") for ln in (tmp_path / "out.csv").read_text().strip().splitlines()[1:]]
+    assert [int(x[0]) for x in rows] == [64, 128]
+    ids = np.fromfile(tmp_path / "ids.bin", dtype=np.int32).reshape(len(c.queries), k)     # the last sweep point
+    if metric == "ip":
+        # the driver normalised scaled copies; normalise the same way before asking the oracle
+        b = (c.base * scale).astype(np.float32)
+        q = (c.queries * qscale).astype(np.float32)
+        for arr in (b, q):                           # reference src/uni.cpp:38-54, float32 throughout
+            n2 = np.cumsum(arr * arr, axis=1, dtype=np.float32)[:, -1]      # sequential float32 sum
+            inv = (np.float32(1.0) / np.sqrt(n2, dtype=np.float32)).astype(np.float32)
+            arr *= inv[:, None]
+    else:
+        b, q = c.base, c.queries
+    ref_ids, _, st = oracle.search(b, c.adj, c.start, q, 128, k, metric)
+    assert np.array_equal(ids, ref_ids)
+    recall, hops = float(rows[1][3]), float(rows[1][4])
+    assert abs(recall - oracle.recall(ref_ids, gt, k)) < 1e-6
+    assert abs(hops - st[:, 4].mean()) < 1e-2 * max(1.0, st[:, 4].mean())
+
+
+def test_driver_reports_errors_instead_of_crashing(tmp_path):
+    build_host.build()
+    exe = os.path.join(os.path.dirname(build_host.HOST_LIB), "test_search_pipeline")
+    r = subprocess.run([exe, "--dataset", "x", "--data_type", "float", "--dist", "l2", "--base_data_path", "/nonexistent",
+                        "--query_path", "/nonexistent", "--gt_path", "/nonexistent"], capture_output=True, text=True)
+    assert r.returncode != 0 and "cannot" in (r.stdout + r.stderr).lower()
+    r = subprocess.run([exe, "--dist", "l2"], capture_output=True, text=True)
+    assert r.returncode != 0 and "required" in r.stderr
