@@ -264,6 +264,7 @@ def main():
         ix.map_ids(gt_ids, id_map)
         torch.cuda.synchronize()
         a_ids, a_d = sharded.all_gather_results(gt_ids, gt_d)
+        torch.cuda.synchronize()               # gathered on torch's streams, merged on the handle's
         gt_ids, _ = ix.merge_shards(a_ids, a_d)
         torch.cuda.synchronize()
 

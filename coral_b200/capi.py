@@ -46,7 +46,7 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    path = _build.build()
+    path = _build.build(checked=os.environ.get("CORAL_B200_CHECKED", "0") == "1")
     lib = C.CDLL(path)
     vp, i32p, f32p, i64p = C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)
     sig = {

@@ -22,6 +22,10 @@ namespace {
 
 thread_local std::string g_create_error;
 
+// Control block shared with the kernel: word 0 = query counter | error flag, word 1 = hop
+// total, words 4..8 = record of the first failed index check (self-checking build only).
+constexpr int kCtrlWords = 16;
+
 struct Options {
     // Defaults from a sweep on 10M x 512 (one B200): many small CTAs beat few large ones, one
     // 256-byte stage per warp beats deeper rings, and shared memory spent on more resident
@@ -342,8 +346,8 @@ int coral_index_create(coral_index_t** out, int device, int64_t n, int dim, int 
     if (e == cudaSuccess) e = cudaEventCreate(&h->ev_k0);
     if (e == cudaSuccess) e = cudaEventCreate(&h->ev_k1);
     if (e == cudaSuccess) e = cudaEventCreate(&h->ev_t1);
-    if (e == cudaSuccess) e = cudaMalloc(&h->d_ctrl, 4 * sizeof(unsigned long long));
-    if (e == cudaSuccess) e = cudaMallocHost(&h->h_ctrl, 4 * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMalloc(&h->d_ctrl, kCtrlWords * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMallocHost(&h->h_ctrl, kCtrlWords * sizeof(unsigned long long));
     if (e == cudaSuccess) e = cudaMalloc(&h->d_hits, sizeof(int64_t));
     if (e != cudaSuccess) {
         cudaGetLastError();
@@ -556,7 +560,7 @@ static int enqueue_search(coral_index* h, const float* d_queries, int Q, int L, 
     SearchPlan p;
     int per_sm = 0;
     if (int rc = get_plan(h, L, p, per_sm)) return rc;
-    CK(cudaMemsetAsync(h->d_ctrl, 0, 4 * sizeof(unsigned long long), st));
+    CK(cudaMemsetAsync(h->d_ctrl, 0, kCtrlWords * sizeof(unsigned long long), st));
     if (Q == 0) return CORAL_OK;
     if ((uint64_t)h->epoch_base + (uint64_t)Q + 2ull >= 0xFFFFFFFFull) {  // epochs would wrap: start over
         CK(cudaMemsetAsync(h->d_ghash, 0, (size_t)h->grid_cap * h->gh_entries * sizeof(uint64_t), st));
@@ -573,6 +577,11 @@ static int enqueue_search(coral_index* h, const float* d_queries, int Q, int L, 
     a.stats_out = d_stats;
     a.q_counter = reinterpret_cast<int*>(h->d_ctrl);
     a.err_flag = reinterpret_cast<int*>(h->d_ctrl) + 1;
+#ifdef CORAL_CHECKED
+    a.dbg = reinterpret_cast<long long*>(h->d_ctrl + 4);
+#else
+    a.dbg = nullptr;
+#endif
     a.hops_total = h->d_ctrl + 1;
     a.ghash = h->d_ghash;
     a.gcand = h->d_gcand;
@@ -593,7 +602,7 @@ static int enqueue_search(coral_index* h, const float* d_queries, int Q, int L, 
     CK(coral::launch_beam_search(a, h->metric, grid, st));
     h->launches += 1;
     h->epoch_base += (uint32_t)Q;
-    CK(cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, st));
+    CK(cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, kCtrlWords * sizeof(unsigned long long), cudaMemcpyDeviceToHost, st));
     return CORAL_OK;
 }
 
@@ -609,6 +618,15 @@ int coral_search_check(coral_index_t* h) {
     if (!h) return CORAL_ERR_ARG;
     const int err = reinterpret_cast<int*>(h->h_ctrl)[1];
     if (err) return fail(h, CORAL_ERR_KERNEL, "a bounded wait in the search kernel ran out; results are invalid");
+#ifdef CORAL_CHECKED
+    const long long* dbg = reinterpret_cast<const long long*>(h->h_ctrl + 4);
+    if (dbg[0] != 0) {
+        char msg[256];
+        std::snprintf(msg, sizeof msg, "index check %lld failed: v0=%lld v1=%lld (0x%llx) query=%lld cta=%lld", dbg[0],
+                      dbg[1], dbg[2], (unsigned long long)dbg[2], dbg[3], dbg[4]);
+        return fail(h, CORAL_ERR_KERNEL, msg);
+    }
+#endif
     return CORAL_OK;
 }
 

@@ -40,6 +40,24 @@ constexpr uint32_t kEmpty32 = 0xFFFFFFFFu;
 constexpr uint64_t kPadKey = 0xFFFFFFFFFFFFFFFFull;
 constexpr long long kWaitClocks = 4000000000ll;  // ~2 s: far beyond any legitimate copy latency
 
+// Self-checking build (-DCORAL_CHECKED): every index that addresses memory is tested first;
+// the first failure is recorded (code, two values, query, CTA) and the access skipped, so a
+// wrong index shows up as CORAL_ERR_KERNEL with its values instead of a device fault.
+#ifdef CORAL_CHECKED
+__device__ __noinline__ bool check_failed(long long* dbg, int code, long long v0, long long v1, int qid) {
+    if (dbg && atomicCAS((unsigned long long*)&dbg[0], 0ull, (unsigned long long)code) == 0ull) {
+        dbg[1] = v0;
+        dbg[2] = v1;
+        dbg[3] = qid;
+        dbg[4] = blockIdx.x;
+    }
+    return false;
+}
+#define CORAL_CHECK(cond, code, v0, v1) ((cond) ? true : check_failed(a.dbg, (code), (long long)(v0), (long long)(v1), S.qid))
+#else
+#define CORAL_CHECK(cond, code, v0, v1) (true)
+#endif
+
 struct Control {
     int qid;
     int exp_count;
@@ -349,7 +367,9 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
             for (int i = tid; i < beam_cnt; i += nthreads) {
                 const uint64_t key = beam[i];
                 if ((key & 1ull) == 0ull) {
-                    exp_list[atomicAdd(&S.exp_count, 1)] = key_id(key);
+                    const int slot = atomicAdd(&S.exp_count, 1);
+                    if (CORAL_CHECK(slot < a.L && key_id(key) >= 0 && (int64_t)key_id(key) < a.n, 1, slot, key))
+                        exp_list[slot] = key_id(key);
                     beam[i] = key | 1ull;
                 }
             }
@@ -370,7 +390,8 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                     while (formed - done < 2u && (pend_n >= 32 || (!more && pend_n > 0))) {
                         const int m = pend_n < 32 ? pend_n : 32;
                         const int slot = formed & 1u;
-                        if (lane < m) bids[slot * 32 + lane] = pend[pend_n - m + lane];
+                        if (lane < m && CORAL_CHECK(pend_n - m + lane >= 0 && pend_n - m + lane < kPendCap, 2, pend_n, m))
+                            bids[slot * 32 + lane] = pend[pend_n - m + lane];
                         if (slot) bcnt1 = m; else bcnt0 = m;
                         pend_n -= m;
                         ++formed;
@@ -383,7 +404,8 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                         if (lane == 0) mbar_expect_tx(&bars[st], (uint32_t)cnt * (uint32_t)P.chunk_bytes);
                         __syncwarp();
                         if (lane < cnt) {
-                            const int id = bids[(b & 1u) * 32 + lane];
+                            int id = bids[(b & 1u) * 32 + lane];
+                            if (!CORAL_CHECK(id >= 0 && (int64_t)id < a.n && cnt <= 32 && (int)st < P.stages, 3, id, cnt)) id = 0;
                             bulk_g2s(stage0 + (size_t)st * P.stage_bytes + (size_t)lane * P.row_stride,
                                      reinterpret_cast<const unsigned char*>(a.vecs) + (size_t)id * row_bytes +
                                          (size_t)c * P.chunk_bytes,
@@ -407,8 +429,11 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                             const int slot = lane + 32 * t;
                             const int ent = e0 + (slot >> a.deg_shift);
                             v[t] = -1;
-                            if (ent < exp_count)
-                                v[t] = __ldg(a.adj + (size_t)exp_list[ent] * a.deg_pad + (slot & (a.deg_pad - 1)));
+                            if (ent < exp_count) {
+                                const int node = exp_list[ent];
+                                if (CORAL_CHECK(ent < a.L && node >= 0 && (int64_t)node < a.n, 4, node, ent))
+                                    v[t] = __ldg(a.adj + (size_t)node * a.deg_pad + (slot & (a.deg_pad - 1)));
+                            }
                         }
                         bool isnew[kIdsPerLane];
 #pragma unroll
@@ -425,7 +450,8 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
 #pragma unroll
                         for (int t = 0; t < kIdsPerLane; ++t) {
                             const uint32_t m = __ballot_sync(0xffffffffu, isnew[t]);
-                            if (isnew[t]) pend[pend_n + __popc(m & lt_mask)] = v[t];
+                            if (isnew[t] && CORAL_CHECK(pend_n + __popc(m & lt_mask) < kPendCap, 5, pend_n, m))
+                                pend[pend_n + __popc(m & lt_mask)] = v[t];
                             pend_n += __popc(m);
                         }
                         __syncwarp();
@@ -487,7 +513,11 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                     const int i = pos + tid;
                     if (i < C) {
                         const uint64_t key = gcand[i];
-                        if (key < bound) sortbuf[atomicAdd(&S.fill, 1)] = key;
+                        if (key < bound) {
+                            const int slot = atomicAdd(&S.fill, 1);
+                            if (CORAL_CHECK(slot < P.tile_max && key_id(key) >= 0 && (int64_t)key_id(key) < a.n, 6, slot, key))
+                                sortbuf[slot] = key;
+                        }
                     }
                     pos += nthreads;
                     __syncthreads();
@@ -503,12 +533,12 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                 for (int i = tid; i < cnt; i += nthreads) {
                     const uint64_t x = beam[i];
                     const int p = i + lower_bound_u64(sortbuf, fill, x);
-                    if (p < a.L) beam_alt[p] = x;
+                    if (p < a.L && CORAL_CHECK(p >= 0 && p < P.LP, 7, p, i)) beam_alt[p] = x;
                 }
                 for (int j = tid; j < fill; j += nthreads) {
                     const uint64_t x = sortbuf[j];
                     const int p = j + upper_bound_u64(beam, cnt, x);
-                    if (p < a.L) beam_alt[p] = x;
+                    if (p < a.L && CORAL_CHECK(p >= 0 && p < P.LP, 8, p, j)) beam_alt[p] = x;
                 }
                 cnt = cnt + fill < a.L ? cnt + fill : a.L;
                 for (int i = cnt + tid; i < P.LP; i += nthreads) beam_alt[i] = kPadKey;
@@ -525,6 +555,9 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                 if (over) S.worst = dist_of<METRIC>((uint32_t)(beam[a.L - 1] >> 32));  // :573
                 if (S.rounds >= a.max_rounds) S.status = 3;
             }
+            // the sort tiles were written to the staging memory through the generic proxy; the
+            // next round's bulk copies write the same bytes through the async proxy
+            fence_async_smem();
             __syncthreads();
             if (S.status == 3) break;
         }

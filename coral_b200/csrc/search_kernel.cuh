@@ -36,6 +36,7 @@ struct SearchArgs {
     uint64_t* gcand;           // [grid][cand_cap] candidates of the current round
     int* q_counter;            // next query to take
     int* err_flag;             // set when a bounded wait ran out
+    long long* dbg;            // self-checking build only: [0] first failed check, [1..4] its values
     int64_t n;
     int dim, deg_pad, deg_shift, M, Q, L, k;
     uint32_t epoch_base;       // epoch of query q is epoch_base + q + 1 (never 0)

@@ -95,7 +95,8 @@ class ShardedIndex:
             torch.cuda.synchronize()
 
         def merger(all_ids, all_dists):
-            out = self.index.merge_shards(all_ids, all_dists)
+            torch.cuda.synchronize()       # the gathered buffers were produced on torch's streams,
+            out = self.index.merge_shards(all_ids, all_dists)   # the merge runs on the handle's
             torch.cuda.synchronize()
             return out
 
