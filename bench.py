@@ -47,7 +47,10 @@ METRIC = "QPS @ recall@10>=0.95, 10Mx512 IP"
 PEAK_FALLBACK_GBS = 6650.0
 # DRAM bytes moved by one full-size launch, from the single-pass ncu capture recorded in
 # profiles/ (workload, L) -> bytes; absent -> null in the JSON line.
-MEASURED_TRAFFIC = {}
+MEASURED_TRAFFIC = {
+    ("c3", 64): 1.026e12,      # dram__bytes_read 1.00 TB + dram__bytes_write 25.9 GB for 100k queries
+    ("small", 64): 3.369e10,   # 32.29 GB + 1.40 GB for 8192 queries
+}
 
 
 def log(*a):
@@ -393,12 +396,13 @@ def main():
                                        f"replicated index, queries split x{world}"),
                        "l2_policy": "inputs larger than L2 (index %.1f GB per GPU)" % index_gb,
                        "plan": {n_: ix.get_option(n_) for n_ in ("plan_stages", "plan_chunk_bytes", "plan_smem_bytes",
-                                                                  "plan_hash_bits", "plan_ctas_per_sm", "warps")}},
+                                                                  "plan_hash_bits", "plan_ctas_per_sm", "plan_warps")}},
             "e2e": {"value": Q / (e2e_ms * 1e-3), "unit": "queries/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": nq * dim * 4 * world, "d2h_bytes_per_step": (nq * k * 4 + 32) * world},
             "gpu_launches": int(launches * world),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": peak_kind, "traffic": MEASURED_TRAFFIC.get((args.workload, L)),
+                         "peak_source": peak_kind, "traffic": (MEASURED_TRAFFIC.get((args.workload, L))
+                                     if world == 1 and not args.queries and not args.n else None),
                          "algorithmic_bytes_per_step": total_alg, "kernel": "beam_search_kernel",
                          "note": "per GPU (slowest rank); algorithmic bytes = n_dist*dim*4 + n_exp*deg_pad*4 + dim*4 + k*8 per query"},
             "cpu_baseline": cpu,

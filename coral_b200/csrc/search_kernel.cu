@@ -511,17 +511,22 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                 int fill = 0;
                 while (pos < C && fill + nthreads <= P.tile_max) {
                     const int i = pos + tid;
+                    int taken = 0;
                     if (i < C) {
                         const uint64_t key = gcand[i];
                         if (key < bound) {
                             const int slot = atomicAdd(&S.fill, 1);
                             if (CORAL_CHECK(slot < P.tile_max && key_id(key) >= 0 && (int64_t)key_id(key) < a.n, 6, slot, key))
                                 sortbuf[slot] = key;
+                            taken = 1;
                         }
                     }
                     pos += nthreads;
-                    __syncthreads();
-                    fill = S.fill;
+                    // The tile's fill level must be the same number in every thread: it decides
+                    // whether another pass runs.  Reading S.fill back after the barrier would race
+                    // with the next pass's atomicAdd of faster threads; the barrier's own count
+                    // cannot.
+                    fill += __syncthreads_count(taken);
                 }
                 if (fill == 0) continue;
                 int n2 = 32;

@@ -97,6 +97,17 @@ def test_tuning_knobs_do_not_change_results(opts):
         assert_same(c, ix, 256, 10)
 
 
+def test_small_sort_tiles_take_many_fill_passes():
+    # Tiny staging memory -> tiny candidate sort tiles -> a round's candidates need many
+    # fill passes; every thread must agree on when a tile is full (barrier-counted).
+    for metric in ("l2", "ip"):
+        c = cases.structured(metric)
+        with make_index(c, len(c.queries), 512, 10, options={"chunk_bytes": 16, "warps": 4}) as ix:
+            for _ in range(3):
+                assert_same(c, ix, 512, 10)
+                assert_same(c, ix, 256, 10)
+
+
 def test_visited_overflow_sets_status_without_fault():
     c = cases.structured("l2")
     with make_index(c, len(c.queries), 64, 10, options={"smem_hash_bits": 0, "ghash_entries": 256}) as ix:
