@@ -348,16 +348,46 @@ def build_graph(base: torch.Tensor, train: torch.Tensor, metric: str, max_degree
             dcell = torch.cdist(cent, cc)
             dcell.fill_diagonal_(float("inf"))
             near = torch.topk(dcell, n_near, dim=1, largest=False).indices      # [cells, n_near]
-            near_rep = rep[near]                                                  # [cells, n_near]
+            # Nearest-cell lists are lopsided in high dimension (a few hub cells are everybody's
+            # neighbour, others nobody's), so a cell also links back to every cell that lists it:
+            # otherwise whole cells have no in-edge and cannot be reached from the entry points.
+            src_c = torch.arange(n_cells, device=dev)[:, None].expand(-1, n_near).reshape(-1)
+            dst_c = near.reshape(-1)
+            # priority: back-links to the cells whose two nearest cells we are (their guaranteed
+            # way in), then our own nearest cells, then the remaining back-links
+            col_c = torch.arange(n_near, device=dev)[None, :].expand(n_cells, -1).reshape(-1)
+            e_src = torch.cat([dst_c, src_c, dst_c])
+            e_dst = torch.cat([src_c, dst_c, src_c])
+            e_cls = torch.cat([torch.where(col_c < 2, 0, 3), torch.ones_like(col_c), torch.full_like(col_c, 2)])
+            ok_e = live[e_src] & live[e_dst] & (e_cls < 3)
+            e_src, e_dst, e_cls = e_src[ok_e], e_dst[ok_e], e_cls[ok_e]
+            o_c = torch.argsort(e_cls, stable=True)
+            e_src, e_dst, e_cls = e_src[o_c], e_dst[o_c], e_cls[o_c]
+            o_c = torch.argsort(e_src * n_cells + e_dst, stable=True)           # duplicates: lowest class first
+            e_src, e_dst, e_cls = e_src[o_c], e_dst[o_c], e_cls[o_c]
+            first_c = torch.ones_like(e_src, dtype=torch.bool)
+            first_c[1:] = (e_src[1:] != e_src[:-1]) | (e_dst[1:] != e_dst[:-1])
+            e_src, e_dst, e_cls = e_src[first_c], e_dst[first_c], e_cls[first_c]
+            o_c = torch.argsort(e_src * 4 + e_cls, stable=True)                 # per source: by class
+            e_src, e_dst = e_src[o_c], e_dst[o_c]
+            start_c = torch.zeros(n_cells + 1, dtype=torch.int64, device=dev)
+            start_c[1:] = torch.cumsum(torch.bincount(e_src, minlength=n_cells), 0)
+            rank_c = torch.arange(e_src.shape[0], device=dev) - start_c[e_src]
+            width_c = 8 * n_near
+            keep_c = rank_c < width_c
+            near_sym = torch.full((n_cells, width_c), -1, dtype=torch.int64, device=dev)
+            near_sym[e_src[keep_c], rank_c[keep_c]] = e_dst[keep_c]
+            n_links = (near_sym >= 0).sum(1).clamp_(min=1)                         # [cells]
+            near_rep = torch.where(near_sym >= 0, rep[near_sym.clamp(min=0)], torch.full_like(near_sym, -1))
             ll = min(long_links, n_near)
-            pick = (torch.arange(n, device=dev)[:, None] * 7 + torch.arange(ll, device=dev)[None, :] * (n_near // ll)) % n_near
+            node = torch.arange(n, device=dev)[:, None]
+            pick = (node * 7 + torch.arange(ll, device=dev)[None, :] * 5) % n_links[assign][:, None]
             longs = near_rep[assign[:, None].expand(-1, ll), pick].to(torch.int32)        # [N, ll]
-            rep_rows = near_rep[live].to(torch.int32)                                     # [live cells, n_near]
+            rep_rows = near_rep[live][:, :max(1, max_degree // 2)].to(torch.int32)        # [live cells, <= R/2]
             rep_ids = rep[live]
         else:
             longs = torch.full((n, 0), -1, dtype=torch.int32, device=dev)
             rep_rows = rep_ids = None
-        del assign
 
         # ---- per node: links to other cells, projection edges, then cell edges; duplicates
         # of an earlier entry are dropped and the row cut to max_degree
@@ -403,14 +433,40 @@ def build_graph(base: torch.Tensor, train: torch.Tensor, metric: str, max_degree
         start_ids = torch.unique(kmeans_nearest(4 * n_start, seed + 1)[0])[:n_start]
         if routers and n > 4 * n_start * max_degree:
             rt, rcent = kmeans_nearest(n_start * max_degree, seed + 2)
-            # a router first points at the representatives of the cells closest (query-to-base
-            # metric) to its query centroid, then keeps what is left of its own row
+            # A router first points at cell representatives, then keeps what is left of its own
+            # row.  Which representatives: for every training query, the routers the search would
+            # rank best for it (query-to-base metric, as the kernel does) are pointed at the
+            # representative of the cell holding that query's nearest base point; a router keeps
+            # its most frequent targets and fills up with the cells closest to its query centroid.
             if rep_ids is not None:
                 n_rep = min(max_degree // 2, rep_ids.shape[0])
-                rep_links = rep_ids[torch.topk(_scores(rcent, base[rep_ids], metric), n_rep, dim=1).indices]
+                rt_vecs = base[rt]
+                want = rep[assign[train_knn[:, 0].long()]]                      # [T] target representative
+                r_l, t_l = [], []
+                for s in range(0, train.shape[0], 8192):
+                    top_r = torch.topk(_scores(train[s:s + 8192], rt_vecs, metric), min(3, rt.shape[0]), dim=1).indices
+                    r_l.append(top_r.reshape(-1))
+                    t_l.append(want[s:s + 8192, None].expand(-1, top_r.shape[1]).reshape(-1))
+                pair = torch.cat(r_l) * n + torch.cat(t_l)
+                pair = pair[torch.cat(t_l) >= 0]
+                uniq, cnt_p = torch.unique(pair, return_counts=True)
+                o_p = torch.argsort(cnt_p, descending=True, stable=True)
+                uniq = uniq[o_p]
+                o_p = torch.argsort(uniq // n, stable=True)
+                uniq = uniq[o_p]
+                r_of, t_of = uniq // n, uniq % n
+                start_p = torch.zeros(rt.shape[0] + 1, dtype=torch.int64, device=dev)
+                start_p[1:] = torch.cumsum(torch.bincount(r_of, minlength=rt.shape[0]), 0)
+                rank_p = torch.arange(r_of.shape[0], device=dev) - start_p[r_of]
+                keep_p = rank_p < n_rep
+                learned = torch.full((rt.shape[0], n_rep), -1, dtype=torch.int64, device=dev)
+                learned[r_of[keep_p], rank_p[keep_p]] = t_of[keep_p]
+                nearest = rep_ids[torch.topk(_scores(rcent, base[rep_ids], metric), n_rep, dim=1).indices]
                 for s in range(0, rt.shape[0], row_chunk):
                     r_ = rt[s:s + row_chunk]
-                    adj[r_, :max_degree] = pack_rows([rep_links[s:s + row_chunk].to(torch.int32), adj[r_, :max_degree]])
+                    links = pack_rows([learned[s:s + row_chunk].to(torch.int32),
+                                       nearest[s:s + row_chunk].to(torch.int32)])[:, :n_rep]
+                    adj[r_, :max_degree] = pack_rows([links, adj[r_, :max_degree]])
             rt = torch.unique(rt)
             rt = rt[~torch.isin(rt, start_ids)]
             rows = torch.full((start_ids.shape[0] * max_degree,), -1, dtype=torch.int32, device=dev)
