@@ -42,6 +42,9 @@ WORKLOADS = {
     "c4": dict(n=12_500_000, dim=200, metric="l2", deg=32, groups=10_000, q=100_000, k=100, Ls=[128, 256], train=100_000,
                sharded=True),
     "small": dict(n=1_000_000, dim=512, metric="ip", deg=64, groups=410, q=8_192, k=10, Ls=[64], train=50_000),
+    # small-batch latency on the c3 index: batches of 1, 8, 64, 512 queries, L=128
+    "c5": dict(n=10_000_000, dim=512, metric="ip", deg=64, groups=4096, q=8_192, k=10, Ls=[128], train=100_000,
+               latency=[1, 8, 64, 512]),
 }
 METRIC = "QPS @ recall@10>=0.95, 10Mx512 IP"
 PEAK_FALLBACK_GBS = 6650.0
@@ -183,6 +186,65 @@ def run_reference(args, w, rank, world):
     print(json.dumps(out), flush=True)
 
 
+def run_latency(args, w, ix, ds, g, device, rank):
+    """Small-batch latency: per batch size, p50/p99 over many batches, device-resident (CUDA events
+    around coral_search_async) and end to end (coral_search, pinned host queries in, host ids out)."""
+    import numpy as np
+    import torch
+    from coral_b200 import capi, synth
+    L, k, dim = args.L or w["Ls"][0], w["k"], w["dim"]
+    lib, handle = capi.load(), ix._h
+    n_gt = 2000
+    gt = synth.exact_knn(ds.base, ds.test[:n_gt], k, w["metric"])
+    ids, _, _, _ = ix.search(ds.test[:n_gt], L, k, dists=False)
+    recall = ix.count_hits(ids, gt, k) / float(k * n_gt)
+    stream = torch.cuda.Stream(device=device)
+    h_all = ds.test.cpu().pin_memory()
+    table = {}
+    launches0 = ix.launch_count
+    for B in w["latency"]:
+        d_ids = torch.empty((B, k), dtype=torch.int32, device=device)
+        h_ids = torch.empty((B, k), dtype=torch.int32).pin_memory()
+        n_batches = max(20, min(200, w["q"] // B))
+        dev_us, e2e_us = [], []
+        hops = C.c_int64(0)
+        for i in range(n_batches + args.warmup):
+            s = (i * B) % (w["q"] - B + 1)
+            q = ds.test[s:s + B]
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record(stream)
+            ix.search_async(q, L, k, d_ids, None, None, stream.cuda_stream)
+            ev1.record(stream)
+            stream.synchronize()
+            hq = h_all[s:s + B].numpy()
+            t0 = time.perf_counter()
+            rc = lib.coral_search(handle, C.c_void_p(hq.ctypes.data), B, L, k, C.c_void_p(h_ids.numpy().ctypes.data),
+                                  None, None, C.byref(hops))
+            t1 = time.perf_counter()
+            if rc != 0:
+                raise RuntimeError(lib.coral_last_error(handle).decode())
+            if i >= args.warmup:
+                dev_us.append(ev0.elapsed_time(ev1) * 1e3)
+                e2e_us.append((t1 - t0) * 1e6)
+        ix.check()
+        table[B] = {"p50_us": float(np.percentile(dev_us, 50)), "p99_us": float(np.percentile(dev_us, 99)),
+                    "e2e_p50_us": float(np.percentile(e2e_us, 50)), "e2e_p99_us": float(np.percentile(e2e_us, 99)),
+                    "qps": B / float(np.percentile(dev_us, 50)) * 1e6, "batches": n_batches,
+                    "ctas_per_query": ix.get_option("last_cluster_size")}
+    if rank == 0:
+        b1 = table[w["latency"][0]]
+        out = {"metric": "p50 latency of one query batch, 10Mx512 IP, L=%d" % L, "value": b1["p50_us"], "unit": "us",
+               "n_gpus": 1, "steps": b1["batches"], "warmup": args.warmup, "ms_per_step": b1["p50_us"] * 1e-3,
+               "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+               "config": {"workload": args.workload, "n": w["n"], "dim": dim, "metric": w["metric"], "max_degree": w["deg"],
+                          "k": k, "L": L, "recall": recall, "batch_sizes": w["latency"], "latency": table,
+                          "l2_policy": "inputs larger than L2; every batch uses different queries"},
+               "e2e": {"value": b1["e2e_p50_us"], "unit": "us", "h2d_bytes_per_step": dim * 4 * w["latency"][0],
+                       "d2h_bytes_per_step": k * 4 * w["latency"][0] + 32},
+               "gpu_launches": int(ix.launch_count - launches0)}
+        print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -260,6 +322,11 @@ def main():
     ix.prepare(max(nq, n_gt), max(w["Ls"] + [args.L]), k)
     torch.cuda.synchronize()
     sh = sharded.ShardedIndex(ix, id_map) if sharded_mode else None
+
+    if w.get("latency"):
+        run_latency(args, w, ix, ds, g, device, rank)
+        ix.close()
+        return
 
     # ---- ground truth (exact, fp32) for the first n_gt queries; global across shards when sharded
     gt_ids, gt_d = exact_topk(ds.base, ds.test[:n_gt], k, w["metric"])

@@ -38,6 +38,7 @@ struct Options {
     int ghash_factor = 8;  // global visited table entries >= factor * L * deg_pad
     int ghash_entries = 0; // explicit table size (power of two >= 64), 0 = from ghash_factor
     int max_rounds = 1 << 16;
+    int cluster_size = 0;  // CTAs sharing one query in small batches: 0 = automatic, 1 = never, else 2/4/8/16
 };
 
 }  // namespace
@@ -66,6 +67,9 @@ struct coral_index {
     uint32_t epoch_base = 0;
     uint64_t* d_ghash = nullptr;
     uint64_t* d_gcand = nullptr;
+    coral::ClusterCtl* d_cctl = nullptr;  // small-batch (cluster) mode: per-cluster round state
+    int32_t* d_gexp = nullptr;            // and expansion lists
+    int last_cluster_size = 1;
     size_t cand_cap_alloc = 0;
     float* d_queries = nullptr;
     int32_t* d_ids = nullptr;
@@ -314,6 +318,8 @@ int ensure_device(coral_index* h) {
 void free_search(coral_index* h) {
     cudaFree(h->d_ghash);   h->d_ghash = nullptr;
     cudaFree(h->d_gcand);   h->d_gcand = nullptr;
+    cudaFree(h->d_cctl);    h->d_cctl = nullptr;
+    cudaFree(h->d_gexp);    h->d_gexp = nullptr;
     cudaFree(h->d_queries); h->d_queries = nullptr;
     cudaFree(h->d_ids);     h->d_ids = nullptr;
     cudaFree(h->d_dists);   h->d_dists = nullptr;
@@ -496,6 +502,7 @@ int coral_set_option(coral_index_t* h, const char* name, int value) {
     else if (s == "ghash_factor") o.ghash_factor = value;
     else if (s == "ghash_entries") o.ghash_entries = value;
     else if (s == "max_rounds") o.max_rounds = value;
+    else if (s == "cluster_size") o.cluster_size = value;
     else return fail(h, CORAL_ERR_ARG, "unknown option " + s);
     h->plans.clear();
     return CORAL_OK;
@@ -513,6 +520,8 @@ int coral_get_option(coral_index_t* h, const char* name, int* value) {
     else if (s == "ghash_factor") *value = o.ghash_factor;
     else if (s == "ghash_entries") *value = (int)h->gh_entries;
     else if (s == "max_rounds") *value = o.max_rounds;
+    else if (s == "cluster_size") *value = o.cluster_size;
+    else if (s == "last_cluster_size") *value = h->last_cluster_size;
     else if (s == "grid_cap") *value = h->grid_cap;
     else if (s == "deg_pad") *value = h->deg_pad;
     else if (s.rfind("plan_", 0) == 0 && !h->plans.empty()) {  // plan of the most recent L
@@ -563,6 +572,8 @@ int coral_search_prepare(coral_index_t* h, int max_queries, int max_L, int max_k
     CK(cudaMemsetAsync(h->d_ghash, 0, (size_t)h->grid_cap * ent * sizeof(uint64_t), h->stream));
     h->epoch_base = 0;
     CK(cudaMalloc(&h->d_gcand, (size_t)h->grid_cap * h->cand_cap_alloc * sizeof(uint64_t)));
+    CK(cudaMalloc(&h->d_cctl, (size_t)h->sm_count * sizeof(coral::ClusterCtl)));
+    CK(cudaMalloc(&h->d_gexp, (size_t)h->sm_count * max_L * sizeof(int32_t)));
     CK(cudaMalloc(&h->d_queries, (size_t)max_queries * h->dim * sizeof(float)));
     CK(cudaMalloc(&h->d_ids, (size_t)max_queries * max_k * sizeof(int32_t)));
     CK(cudaMalloc(&h->d_dists, (size_t)max_queries * max_k * sizeof(float)));
@@ -620,8 +631,29 @@ static int enqueue_search(coral_index* h, const float* d_queries, int Q, int L, 
     a.cand_cap = (int)std::min<size_t>((size_t)L * h->deg_pad, h->cand_cap_alloc);
     a.max_rounds = h->opt.max_rounds;
     a.plan = p;
-    const int grid = std::min(Q, std::min(h->sm_count * per_sm, h->grid_cap));
-    CK(coral::launch_beam_search(a, h->metric, grid, st));
+    int grid = std::min(Q, std::min(h->sm_count * per_sm, h->grid_cap));
+    // Small batches leave most SMs idle with one CTA per query: let a thread-block cluster of
+    // 2..16 CTAs share each query instead (needs the visited set entirely in the global table).
+    int cs = 1;
+    const int slots = h->sm_count * per_sm;   // CTAs resident at once
+    if (h->opt.cluster_size != 1 && p.hs_bits == 0 && Q <= std::min(slots / 2, h->sm_count)) {
+        // automatic: the largest cluster that still keeps every query's cluster resident
+        cs = h->opt.cluster_size > 1 ? h->opt.cluster_size : 16;
+        while (cs > 1 && (cs > 16 || (cs & (cs - 1)) != 0 || (h->opt.cluster_size <= 1 && Q * cs > slots))) cs >>= 1;
+        int room = 0;
+        while (cs > 1 && ((room = coral::beam_search_max_clusters(p, h->metric, cs)) < 1 ||
+                          (h->opt.cluster_size <= 1 && room < Q)))
+            cs >>= 1;
+        if (cs > 1) {
+            const int groups = std::min(Q, std::min(room, h->sm_count));
+            grid = groups * cs;
+            CK(cudaMemsetAsync(h->d_cctl, 0, (size_t)groups * sizeof(coral::ClusterCtl), st));
+            a.cctl = h->d_cctl;
+            a.gexp = h->d_gexp;
+        }
+    }
+    h->last_cluster_size = cs;
+    CK(coral::launch_beam_search(a, h->metric, grid, st, cs));
     h->launches += 1;
     h->epoch_base += (uint32_t)Q;
     CK(cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, kCtrlWords * sizeof(unsigned long long), cudaMemcpyDeviceToHost, st));

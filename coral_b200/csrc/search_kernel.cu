@@ -113,6 +113,22 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 __device__ __forceinline__ void fence_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// Thread-block cluster helpers (small-batch mode: one cluster per query).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_cta_count() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ int load_shared_int(const int* p) { return *(const volatile int*)p; }
+__device__ __forceinline__ float load_shared_float(const float* p) { return *(const volatile float*)p; }
 
 // "closer" == smaller key.  key = ord(dist):id:expanded-bit.
 template <int METRIC>
@@ -273,7 +289,11 @@ __device__ __forceinline__ float seed_distance(const float* __restrict__ row, co
     return __shfl_sync(0xffffffffu, sum, 0);
 }
 
-template <int METRIC>
+// CLUSTER = false: one CTA per query.  CLUSTER = true (small batches): the CTAs of a thread-block
+// cluster share one query -- the leader CTA (rank 0) owns the beam, builds the expansion list and
+// merges; every CTA runs the scout/gather/distance pipeline against the shared global visited
+// table, work counter and candidate buffer; two cluster barriers per round.
+template <int METRIC, bool CLUSTER>
 __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ Control S;
@@ -294,8 +314,20 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
     unsigned char* stage0 = smem + P.off_stage + (size_t)warp * P.stages * P.stage_bytes;
     uint64_t* sortbuf = reinterpret_cast<uint64_t*>(smem + P.off_stage);  // aliases the staging rings
 
-    uint64_t* ghash = a.ghash + (size_t)blockIdx.x * ((size_t)a.gh_mask + 1);
-    uint64_t* gcand = a.gcand + (size_t)blockIdx.x * (size_t)a.cand_cap;
+    int group = blockIdx.x, n_groups = gridDim.x;   // a group = the CTAs working on one query
+    bool leader = true;
+    if (CLUSTER) {
+        const int csize = (int)cluster_cta_count();
+        group = blockIdx.x / csize;
+        n_groups = gridDim.x / csize;
+        leader = cluster_cta_rank() == 0;
+    }
+    ClusterCtl* GC = CLUSTER ? a.cctl + group : nullptr;
+    int32_t* gexp = CLUSTER ? a.gexp + (size_t)group * a.L : nullptr;
+    uint64_t* ghash = a.ghash + (size_t)group * ((size_t)a.gh_mask + 1);
+    uint64_t* gcand = a.gcand + (size_t)group * (size_t)a.cand_cap;
+    int* p_exp_next = CLUSTER ? &GC->exp_next : &S.exp_next;
+    int* p_cand_count = CLUSTER ? &GC->cand_count : &S.cand_count;
 
     if (lane == 0)
         for (int s = 0; s < P.stages; ++s) mbar_init(&bars[s], 1);
@@ -312,17 +344,20 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
     const int G = 128 >> a.deg_shift;  // beam entries covered by one scout step
     const int row_bytes = a.dim * 4;
 
-    for (;;) {
+    for (int turn = 0;; ++turn) {
         // ---------------------------------------------------------------- take a query
         __syncthreads();
         if (tid == 0) {
             int q = -1;
-            if (*(volatile int*)a.err_flag == 0) q = atomicAdd(a.q_counter, 1);
+            if (CLUSTER)
+                q = group + turn * n_groups;   // static: every CTA of the cluster must agree
+            else if (*(volatile int*)a.err_flag == 0)
+                q = atomicAdd(a.q_counter, 1);
             if (q >= a.Q) q = -1;
             S.qid = q;
             S.status = 0;
             S.worst = METRIC == 0 ? 3.402823466e+38f : -3.402823466e+38f;
-            S.n_dist = a.M;
+            S.n_dist = leader ? a.M : 0;
             S.n_exp = S.n_scan = S.n_spill = S.hops = S.rounds = S.max_cand = 0;
             S.beam_cnt = a.M;
         }
@@ -341,7 +376,7 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
         bool overflow = false;
 
         // ---------------------------------------------------------------- entry points
-        for (int i = warp; i < a.M; i += (nthreads >> 5)) {
+        for (int i = warp; leader && i < a.M; i += (nthreads >> 5)) {
             const int id = a.start_ids[i];
             if (lane == 0) {
                 const int r = visited_insert(shash, P.hs_bits, ghash, a.gh_mask, epoch, id, n_spill);
@@ -351,31 +386,47 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
             if (lane == 0) beam[i] = make_key<METRIC>(d, id, 0u);
         }
         __syncthreads();
-        bitonic_sort(beam, P.LP, tid, nthreads);
+        if (leader) bitonic_sort(beam, P.LP, tid, nthreads);
 
         // ---------------------------------------------------------------- rounds
+        bool finished = false;   // leader's verdict on the previous round (cluster mode)
         for (;;) {
             // expansion list: every beam entry not yet expanded (src/search_gpu.cu:416-422)
-            if (tid == 0) {
-                S.exp_count = 0;
-                S.exp_next = 0;
-                S.cand_count = 0;
-                S.rounds += 1;
-            }
-            __syncthreads();
-            const int beam_cnt = S.beam_cnt;
-            for (int i = tid; i < beam_cnt; i += nthreads) {
-                const uint64_t key = beam[i];
-                if ((key & 1ull) == 0ull) {
-                    const int slot = atomicAdd(&S.exp_count, 1);
-                    if (CORAL_CHECK(slot < a.L && key_id(key) >= 0 && (int64_t)key_id(key) < a.n, 1, slot, key))
-                        exp_list[slot] = key_id(key);
-                    beam[i] = key | 1ull;
+            if (leader && !finished) {
+                if (tid == 0) {
+                    S.exp_count = 0;
+                    S.exp_next = 0;
+                    S.cand_count = 0;
+                    S.rounds += 1;
                 }
+                __syncthreads();
+                const int beam_cnt = S.beam_cnt;
+                for (int i = tid; i < beam_cnt; i += nthreads) {
+                    const uint64_t key = beam[i];
+                    if ((key & 1ull) == 0ull) {
+                        const int slot = atomicAdd(&S.exp_count, 1);
+                        if (CORAL_CHECK(slot < a.L && key_id(key) >= 0 && (int64_t)key_id(key) < a.n, 1, slot, key)) {
+                            if (CLUSTER) gexp[slot] = key_id(key); else exp_list[slot] = key_id(key);
+                        }
+                        beam[i] = key | 1ull;
+                    }
+                }
+                __syncthreads();
             }
-            __syncthreads();
-            const int exp_count = S.exp_count;
-            const float worst = S.worst;
+            if (CLUSTER) {
+                if (leader && tid == 0) {   // publish the round to the other CTAs
+                    GC->exp_count = S.exp_count;
+                    GC->exp_next = 0;
+                    GC->cand_count = 0;
+                    GC->worst = S.worst;
+                    GC->done = finished ? 1 : 0;
+                }
+                __threadfence();
+                cluster_sync_all();
+                if (load_shared_int(&GC->done)) break;
+            }
+            const int exp_count = CLUSTER ? load_shared_int(&GC->exp_count) : S.exp_count;
+            const float worst = CLUSTER ? load_shared_float(&GC->worst) : S.worst;
 
             // ------------------------------------------------------------ warp pipeline
             {
@@ -416,7 +467,7 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                     if (more && pend_n < 32) {
                         // ---- scout: adjacency rows of up to G entries, visited test-and-set
                         int e0 = 0;
-                        if (lane == 0) e0 = atomicAdd(&S.exp_next, G);
+                        if (lane == 0) e0 = atomicAdd(p_exp_next, G);
                         e0 = __shfl_sync(0xffffffffu, e0, 0);
                         if (e0 >= exp_count) {
                             more = false;
@@ -430,7 +481,7 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                             const int ent = e0 + (slot >> a.deg_shift);
                             v[t] = -1;
                             if (ent < exp_count) {
-                                const int node = exp_list[ent];
+                                const int node = CLUSTER ? __ldcg(gexp + ent) : exp_list[ent];
                                 if (CORAL_CHECK(ent < a.L && node >= 0 && (int64_t)node < a.n, 4, node, ent))
                                     v[t] = __ldg(a.adj + (size_t)node * a.deg_pad + (slot & (a.deg_pad - 1)));
                             }
@@ -479,7 +530,7 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                             int base = 0;
                             if (lane == 0) {
                                 n_dist += cnt;
-                                if (m) base = atomicAdd(&S.cand_count, __popc(m));
+                                if (m) base = atomicAdd(p_cand_count, __popc(m));
                             }
                             base = __shfl_sync(0xffffffffu, base, 0);
                             if (ok) {
@@ -495,12 +546,22 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                     if (!more && pend_n == 0) break;
                 }
             }
-            __syncthreads();
+            if (CLUSTER) {
+                __threadfence();   // candidates written by every CTA must be visible to the leader
+                cluster_sync_all();
+                if (!leader) continue;
+            } else {
+                __syncthreads();
+            }
 
-            // ------------------------------------------------------------ merge
-            int C = S.cand_count;
+            // ------------------------------------------------------------ merge (leader CTA)
+            int C = CLUSTER ? load_shared_int(&GC->cand_count) : S.cand_count;
             if (C > a.cand_cap) C = a.cand_cap;
-            if (C == 0) break;  // converged (src/search_gpu.cu:442)
+            if (C == 0) {  // converged (src/search_gpu.cu:442)
+                if (!CLUSTER) break;
+                finished = true;
+                continue;
+            }
             int cnt = S.beam_cnt;
             const bool over = cnt + C > a.L;
             uint64_t bound = cnt >= a.L ? beam[a.L - 1] : kPadKey;
@@ -513,7 +574,7 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                     const int i = pos + tid;
                     int taken = 0;
                     if (i < C) {
-                        const uint64_t key = gcand[i];
+                        const uint64_t key = __ldcg(gcand + i);
                         if (key < bound) {
                             const int slot = atomicAdd(&S.fill, 1);
                             if (CORAL_CHECK(slot < P.tile_max && key_id(key) >= 0 && (int64_t)key_id(key) < a.n, 6, slot, key))
@@ -564,7 +625,10 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
             // next round's bulk copies write the same bytes through the async proxy
             fence_async_smem();
             __syncthreads();
-            if (S.status == 3) break;
+            if (S.status == 3) {
+                if (!CLUSTER) break;
+                finished = true;
+            }
         }
 
         // ---------------------------------------------------------------- tallies
@@ -581,9 +645,29 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
         }
         if (__any_sync(0xffffffffu, overflow) && lane == 0) atomicMax(&S.status, 2);
         __syncthreads();
+        if (CLUSTER) {   // fold the other CTAs' tallies into the leader's
+            if (!leader && tid == 0) {
+                atomicAdd(&GC->n_scan, S.n_scan);
+                atomicAdd(&GC->n_spill, S.n_spill);
+                atomicAdd(&GC->n_exp, S.n_exp);
+                atomicAdd(&GC->n_dist, S.n_dist);
+                if (S.status == 2) atomicMax(&GC->status, 2);
+            }
+            __threadfence();
+            cluster_sync_all();
+            if (leader && tid == 0) {
+                S.n_scan += load_shared_int(&GC->n_scan);
+                S.n_spill += load_shared_int(&GC->n_spill);
+                S.n_exp += load_shared_int(&GC->n_exp);
+                S.n_dist += load_shared_int(&GC->n_dist);
+                if (load_shared_int(&GC->status) == 2 && S.status < 2) S.status = 2;
+                GC->n_scan = GC->n_spill = GC->n_exp = GC->n_dist = GC->status = 0;
+            }
+            __syncthreads();
+        }
 
         // ---------------------------------------------------------------- top-k out (src/search_gpu.cu:447-472, :716)
-        if (warp == 0) {
+        if (leader && warp == 0) {
             const int cnt = S.beam_cnt;
             const float far0 = METRIC == 0 ? 3.402823466e+38f : -3.402823466e+38f;
             int written = 0;
@@ -627,32 +711,91 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
 
 }  // namespace
 
-cudaError_t launch_beam_search(const SearchArgs& a, int metric, int grid, cudaStream_t stream) {
+namespace {
+template <int METRIC, bool CLUSTER>
+const void* kernel_ptr() {
+    return (const void*)beam_search_kernel<METRIC, CLUSTER>;
+}
+const void* kernel_for(int metric, bool cluster) {
+    if (metric == 0) return cluster ? kernel_ptr<0, true>() : kernel_ptr<0, false>();
+    return cluster ? kernel_ptr<1, true>() : kernel_ptr<1, false>();
+}
+// The opt-in shared-memory limit of each instantiation only ever grows, so plans made for other
+// beam capacities stay launchable.
+bool grant_smem(int metric, bool cluster, int bytes) {
+    static int granted[2][2] = {{0, 0}, {0, 0}};
+    if (bytes <= granted[metric][cluster]) return true;
+    if (cudaFuncSetAttribute(kernel_for(metric, cluster), cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) !=
+        cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    granted[metric][cluster] = bytes;
+    return true;
+}
+}  // namespace
+
+cudaError_t launch_beam_search(const SearchArgs& a, int metric, int grid, cudaStream_t stream, int cluster_size) {
     const int threads = a.plan.warps * 32;
-    if (metric == 0)
-        beam_search_kernel<0><<<grid, threads, a.plan.smem_bytes, stream>>>(a);
-    else
-        beam_search_kernel<1><<<grid, threads, a.plan.smem_bytes, stream>>>(a);
-    return cudaGetLastError();
+    if (cluster_size <= 1) {
+        if (metric == 0)
+            beam_search_kernel<0, false><<<grid, threads, a.plan.smem_bytes, stream>>>(a);
+        else
+            beam_search_kernel<1, false><<<grid, threads, a.plan.smem_bytes, stream>>>(a);
+        return cudaGetLastError();
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3((unsigned)threads, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)a.plan.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster_size;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (metric == 0) return cudaLaunchKernelEx(&cfg, beam_search_kernel<0, true>, a);
+    return cudaLaunchKernelEx(&cfg, beam_search_kernel<1, true>, a);
 }
 
 int beam_search_occupancy(const SearchPlan& p, int metric) {
-    const void* fn = metric == 0 ? (const void*)beam_search_kernel<0> : (const void*)beam_search_kernel<1>;
-    // The opt-in limit only ever grows: plans for other beam capacities stay launchable.
-    static int granted[2] = {0, 0};
-    if (p.smem_bytes > granted[metric]) {
-        if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, p.smem_bytes) != cudaSuccess) {
-            cudaGetLastError();
-            return 0;
-        }
-        granted[metric] = p.smem_bytes;
-    }
+    if (!grant_smem(metric, false, p.smem_bytes)) return 0;
     int nb = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, fn, p.warps * 32, p.smem_bytes) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kernel_for(metric, false), p.warps * 32, p.smem_bytes) !=
+        cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
     return nb;
+}
+
+int beam_search_max_clusters(const SearchPlan& p, int metric, int cluster_size) {
+    if (cluster_size < 2 || !grant_smem(metric, true, p.smem_bytes)) return 0;
+    const void* fn = kernel_for(metric, true);
+    if (cluster_size > 8 &&
+        cudaFuncSetAttribute(fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)cluster_size, 1, 1);
+    cfg.blockDim = dim3((unsigned)(p.warps * 32), 1, 1);
+    cfg.dynamicSmemBytes = (size_t)p.smem_bytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster_size;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, fn, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
 }
 
 }  // namespace coral

@@ -22,6 +22,15 @@ struct SearchPlan {
     int smem_bytes;
 };
 
+// Round state shared by the CTAs of a thread-block cluster that work on one query
+// (small-batch mode); lives in global memory, one block per cluster.
+struct ClusterCtl {
+    int exp_count, exp_next, cand_count, done;
+    float worst;
+    int n_dist, n_exp, n_scan, n_spill, status;
+    int pad[6];
+};
+
 struct SearchArgs {
     const float* vecs;         // [n][dim]
     const int32_t* adj;        // [n][deg_pad]
@@ -37,6 +46,8 @@ struct SearchArgs {
     int* q_counter;            // next query to take
     int* err_flag;             // set when a bounded wait ran out
     long long* dbg;            // self-checking build only: [0] first failed check, [1..4] its values
+    ClusterCtl* cctl;          // cluster mode: [clusters] round state
+    int32_t* gexp;             // cluster mode: [clusters][L] ids to expand this round
     int64_t n;
     int dim, deg_pad, deg_shift, M, Q, L, k;
     uint32_t epoch_base;       // epoch of query q is epoch_base + q + 1 (never 0)
@@ -46,10 +57,15 @@ struct SearchArgs {
     SearchPlan plan;
 };
 
-// Launches the kernel for `metric` (0 = L2, 1 = IP) with `grid` CTAs on `stream`.
-cudaError_t launch_beam_search(const SearchArgs& a, int metric, int grid, cudaStream_t stream);
+// Launches the kernel for `metric` (0 = L2, 1 = IP) with `grid` CTAs on `stream`.  With
+// cluster_size > 1 the grid is made of thread-block clusters of that many CTAs, each cluster
+// working on one query at a time (grid must be a multiple of cluster_size).
+cudaError_t launch_beam_search(const SearchArgs& a, int metric, int grid, cudaStream_t stream, int cluster_size = 1);
 // Registers the dynamic shared-memory size with the runtime and returns the
 // number of CTAs of this plan that fit one SM (0 on failure).
 int beam_search_occupancy(const SearchPlan& p, int metric);
+// Number of clusters of `cluster_size` CTAs of this plan that can be resident at once (0 when
+// that cluster size cannot be launched).
+int beam_search_max_clusters(const SearchPlan& p, int metric, int cluster_size);
 
 }  // namespace coral

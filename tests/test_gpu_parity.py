@@ -27,15 +27,22 @@ def make_index(c, max_q, max_L, max_k, options=None, device_vectors=False):
     return ix
 
 
-def assert_same(c, ix, L, k, queries=None, check_stats=True):
+def assert_same(c, ix, L, k, queries=None, check_stats=True, modes=(1, 0)):
+    """Search and compare with the oracle.  The test batches are small, so by default each check
+    runs twice: one CTA per query (cluster_size 1) and the automatic small-batch mode in which a
+    thread-block cluster shares each query.  modes=None leaves the handle's setting alone."""
     q = c.queries if queries is None else queries
     ref_ids, ref_d, ref_st = oracle.search(c.base, c.adj, c.start, q, L, k, c.metric)
-    ids, d, st, hops = ix.search(q, L, k, dists=True, stats=True)
-    assert np.array_equal(ids, ref_ids), f"{c.name} L={L} k={k}: ids differ"
-    assert np.array_equal(d.view(np.uint32), ref_d.view(np.uint32)), f"{c.name} L={L} k={k}: distances differ"
-    if check_stats:
-        assert np.array_equal(st[:, :7], ref_st[:, :7]), f"{c.name} L={L} k={k}: counters differ"
-        assert hops == int(ref_st[:, 4].sum())
+    for mode in (modes or (None,)):
+        if mode is not None:
+            ix.set_option("cluster_size", mode)
+        ids, d, st, hops = ix.search(q, L, k, dists=True, stats=True)
+        tag = f"{c.name} L={L} k={k} cluster_size={mode}"
+        assert np.array_equal(ids, ref_ids), f"{tag}: ids differ"
+        assert np.array_equal(d.view(np.uint32), ref_d.view(np.uint32)), f"{tag}: distances differ"
+        if check_stats:
+            assert np.array_equal(st[:, :7], ref_st[:, :7]), f"{tag}: counters differ"
+            assert hops == int(ref_st[:, 4].sum())
     return ids, d, st, ref_st
 
 
@@ -106,6 +113,26 @@ def test_small_sort_tiles_take_many_fill_passes():
             for _ in range(3):
                 assert_same(c, ix, 512, 10)
                 assert_same(c, ix, 256, 10)
+
+
+@pytest.mark.parametrize("metric", ["l2", "ip"])
+def test_small_batches_share_a_query_across_a_cluster(metric):
+    # Batches far below the SM count run one thread-block cluster per query; results and
+    # counters must not depend on how many CTAs cooperate.
+    c = cases.structured(metric)
+    with make_index(c, len(c.queries), 128, 10) as ix:
+        for nq in (1, 3, 8, 20, 70):
+            assert_same(c, ix, 64, 10, queries=c.queries[:nq], modes=(0,))
+            assert 2 <= ix.get_option("last_cluster_size") <= 16
+        assert_same(c, ix, 128, 10, queries=c.queries[:5], modes=(0,))
+        assert_same(c, ix, 64, 10, modes=(0,))                  # the whole batch of 96
+    for size in (2, 8, 16):
+        with make_index(c, len(c.queries), 128, 10, options={"cluster_size": size}) as ix:
+            assert_same(c, ix, 128, 10, queries=c.queries[:9], modes=None)
+            assert ix.get_option("last_cluster_size") in (size, size // 2)
+    with make_index(c, len(c.queries), 128, 10, options={"cluster_size": 1}) as ix:
+        assert_same(c, ix, 128, 10, queries=c.queries[:2], modes=None)
+        assert ix.get_option("last_cluster_size") == 1
 
 
 def test_visited_overflow_sets_status_without_fault():
