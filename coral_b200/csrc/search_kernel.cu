@@ -341,7 +341,11 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
     const int n_chunks = P.n_chunks;
     const int chunk_vec = P.chunk_bytes >> 4;
     const int chunk_floats = P.chunk_bytes >> 2;
-    const int G = 128 >> a.deg_shift;  // beam entries covered by one scout step
+    // A scout step takes the next 32 * ids_per_lane neighbour slots of the round's expansion list
+    // (slot = entry * deg_pad + column).  Large steps amortise the latency of a step when a CTA has
+    // many entries to itself; small steps spread a short list over the many warps of a cluster.
+    const int ipl = a.ids_per_lane < 1 ? kIdsPerLane : (a.ids_per_lane > kIdsPerLane ? kIdsPerLane : a.ids_per_lane);
+    const int step_slots = 32 * ipl;
     const int row_bytes = a.dim * 4;
 
     for (int turn = 0;; ++turn) {
@@ -466,21 +470,25 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                     }
                     if (more && pend_n < 32) {
                         // ---- scout: adjacency rows of up to G entries, visited test-and-set
-                        int e0 = 0;
-                        if (lane == 0) e0 = atomicAdd(p_exp_next, G);
-                        e0 = __shfl_sync(0xffffffffu, e0, 0);
-                        if (e0 >= exp_count) {
+                        int s0 = 0;
+                        if (lane == 0) s0 = atomicAdd(p_exp_next, step_slots);
+                        s0 = __shfl_sync(0xffffffffu, s0, 0);
+                        const int total_slots = exp_count << a.deg_shift;
+                        if (s0 >= total_slots) {
                             more = false;
                             continue;
                         }
-                        if (lane == 0) n_exp += (exp_count - e0 < G) ? exp_count - e0 : G;
+                        if (lane == 0) {   // entries whose first slot falls into this step
+                            const int s1 = s0 + step_slots < total_slots ? s0 + step_slots : total_slots;
+                            n_exp += ((s1 + a.deg_pad - 1) >> a.deg_shift) - ((s0 + a.deg_pad - 1) >> a.deg_shift);
+                        }
                         int v[kIdsPerLane];
 #pragma unroll
                         for (int t = 0; t < kIdsPerLane; ++t) {
-                            const int slot = lane + 32 * t;
-                            const int ent = e0 + (slot >> a.deg_shift);
+                            const int slot = s0 + lane + 32 * t;
+                            const int ent = slot >> a.deg_shift;
                             v[t] = -1;
-                            if (ent < exp_count) {
+                            if (t < ipl && ent < exp_count) {
                                 const int node = CLUSTER ? __ldcg(gexp + ent) : exp_list[ent];
                                 if (CORAL_CHECK(ent < a.L && node >= 0 && (int64_t)node < a.n, 4, node, ent))
                                     v[t] = __ldg(a.adj + (size_t)node * a.deg_pad + (slot & (a.deg_pad - 1)));

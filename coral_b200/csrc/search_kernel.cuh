@@ -53,6 +53,7 @@ struct SearchArgs {
     uint32_t epoch_base;       // epoch of query q is epoch_base + q + 1 (never 0)
     uint32_t gh_mask;
     int cand_cap;              // L * deg_pad
+    int ids_per_lane;          // neighbour ids a lane examines per scout step, 1..4 (0 = 4)
     int max_rounds;
     SearchPlan plan;
 };

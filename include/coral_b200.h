@@ -130,7 +130,8 @@ int64_t coral_launch_count(coral_index_t* h);
  * "chunk_bytes", "stages", "smem_hash_bits" (0 = visited set entirely in the
  * global table), "ghash_factor", "ghash_entries", "max_rounds", "cluster_size" (CTAs that
  * share one query when the batch is far smaller than the GPU: 0 = automatic, 1 = never,
- * 2/4/8/16 = forced; results do not depend on it).  Returns CORAL_ERR_ARG for unknown names. */
+ * 2/4/8/16 = forced; results do not depend on it), "scout_ids" (neighbour ids a lane examines
+ * per scout step, 1..4, 0 = automatic).  Returns CORAL_ERR_ARG for unknown names. */
 int coral_set_option(coral_index_t* h, const char* name, int value);
 int coral_get_option(coral_index_t* h, const char* name, int* value);
 

@@ -96,6 +96,8 @@ def test_underfull_beam_is_reported_not_faulted():
     {"warps": 8, "ctas_per_sm": 1, "chunk_bytes": 512},
     {"warps": 2, "ctas_per_sm": 4, "chunk_bytes": 64, "stages": 3},
     {"warps": 3, "ctas_per_sm": 1, "chunk_bytes": 2048},
+    {"scout_ids": 1},                              # 32 neighbour slots per scout step (half an adjacency row)
+    {"scout_ids": 3, "warps": 5},
 ])
 def test_tuning_knobs_do_not_change_results(opts):
     c = cases.structured("ip")
