@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "../../include/coral_b200.h"
+#include "schedule.cuh"
 #include "search_kernel.cuh"
 
 using coral::SearchArgs;
@@ -25,6 +26,7 @@ thread_local std::string g_create_error;
 // Control block shared with the kernel: word 0 = query counter | error flag, word 1 = hop
 // total, words 4..8 = record of the first failed index check (self-checking build only).
 constexpr int kCtrlWords = 16;
+constexpr int kMaxFrontier = 4096;   // entry points' neighbours used by the scheduling pre-pass
 
 struct Options {
     // Defaults from a sweep on 10M x 512 (one B200): many small CTAs beat few large ones, one
@@ -40,6 +42,7 @@ struct Options {
     int max_rounds = 1 << 16;
     int cluster_size = 0;  // CTAs sharing one query in small batches: 0 = automatic, 1 = never, else 2/4/8/16
     int scout_ids = 0;     // neighbour ids per lane per scout step: 0 = automatic (4; 1 in cluster mode), else 1..4
+    int schedule = 0;      // order large batches for L2 locality: 0 = automatic (batches >= 8192), 1 = always, -1 = never
 };
 
 }  // namespace
@@ -71,6 +74,17 @@ struct coral_index {
     coral::ClusterCtl* d_cctl = nullptr;  // small-batch (cluster) mode: per-cluster round state
     int32_t* d_gexp = nullptr;            // and expansion lists
     int last_cluster_size = 1;
+    // locality scheduling: the entry points' neighbours ("frontier") and per-batch scratch
+    std::vector<int32_t> h_start;
+    bool frontier_dirty = true;
+    int n_front = 0;
+    int32_t* d_front_ids = nullptr;
+    float* d_front_vecs = nullptr;
+    float* d_front_norm = nullptr;
+    int* d_keys = nullptr;
+    int* d_bins = nullptr;
+    int32_t* d_order = nullptr;
+    int last_scheduled = 0;
     size_t cand_cap_alloc = 0;
     float* d_queries = nullptr;
     int32_t* d_ids = nullptr;
@@ -327,6 +341,9 @@ void free_search(coral_index* h) {
     cudaFree(h->d_gcand);   h->d_gcand = nullptr;
     cudaFree(h->d_cctl);    h->d_cctl = nullptr;
     cudaFree(h->d_gexp);    h->d_gexp = nullptr;
+    cudaFree(h->d_keys);    h->d_keys = nullptr;
+    cudaFree(h->d_bins);    h->d_bins = nullptr;
+    cudaFree(h->d_order);   h->d_order = nullptr;
     cudaFree(h->d_queries); h->d_queries = nullptr;
     cudaFree(h->d_ids);     h->d_ids = nullptr;
     cudaFree(h->d_dists);   h->d_dists = nullptr;
@@ -402,6 +419,9 @@ int coral_index_destroy(coral_index_t* h) {
     cudaFree(h->d_adj);
     cudaFree(h->d_start);
     cudaFree(h->d_deleted);
+    cudaFree(h->d_front_ids);
+    cudaFree(h->d_front_vecs);
+    cudaFree(h->d_front_norm);
     cudaFree(h->d_ctrl);
     cudaFree(h->d_hits);
     if (h->h_ctrl) cudaFreeHost(h->h_ctrl);
@@ -424,6 +444,7 @@ int coral_index_set_vectors(coral_index_t* h, const float* vecs) {
     h->own_vecs = false;
     CK(cudaMalloc(&h->d_vecs, bytes));
     h->own_vecs = true;
+    h->frontier_dirty = true;
     CK(cudaMemcpyAsync(h->d_vecs, vecs, bytes, cudaMemcpyDefault, h->stream));
     CK(cudaStreamSynchronize(h->stream));
     return CORAL_OK;
@@ -437,6 +458,7 @@ int coral_index_attach_vectors(coral_index_t* h, const float* dev_vecs) {
     if (h->own_vecs) cudaFree(h->d_vecs);
     h->d_vecs = const_cast<float*>(dev_vecs);
     h->own_vecs = false;
+    h->frontier_dirty = true;
     return CORAL_OK;
 }
 
@@ -447,6 +469,7 @@ int coral_index_set_adjacency(coral_index_t* h, const int32_t* adj, int deg_pad)
     const size_t bytes = (size_t)h->n * deg_pad * sizeof(int32_t);
     if (!h->d_adj) CK(cudaMalloc(&h->d_adj, bytes));
     CK(cudaMemcpyAsync(h->d_adj, adj, bytes, cudaMemcpyDefault, h->stream));
+    h->frontier_dirty = true;
     CK(cudaStreamSynchronize(h->stream));
     return CORAL_OK;
 }
@@ -479,6 +502,8 @@ int coral_index_set_start_ids(coral_index_t* h, const int32_t* ids, int M) {
     CK(cudaMemcpyAsync(h->d_start, ids, (size_t)M * sizeof(int32_t), cudaMemcpyHostToDevice, h->stream));
     CK(cudaStreamSynchronize(h->stream));
     h->M = M;
+    h->h_start.assign(ids, ids + M);
+    h->frontier_dirty = true;
     return CORAL_OK;
 }
 
@@ -511,6 +536,7 @@ int coral_set_option(coral_index_t* h, const char* name, int value) {
     else if (s == "max_rounds") o.max_rounds = value;
     else if (s == "cluster_size") o.cluster_size = value;
     else if (s == "scout_ids") o.scout_ids = value;
+    else if (s == "schedule") o.schedule = value;
     else return fail(h, CORAL_ERR_ARG, "unknown option " + s);
     h->plans.clear();
     return CORAL_OK;
@@ -530,6 +556,9 @@ int coral_get_option(coral_index_t* h, const char* name, int* value) {
     else if (s == "max_rounds") *value = o.max_rounds;
     else if (s == "cluster_size") *value = o.cluster_size;
     else if (s == "last_cluster_size") *value = h->last_cluster_size;
+    else if (s == "schedule") *value = o.schedule;
+    else if (s == "last_scheduled") *value = h->last_scheduled;
+    else if (s == "frontier_size") *value = h->n_front;
     else if (s == "grid_cap") *value = h->grid_cap;
     else if (s == "deg_pad") *value = h->deg_pad;
     else if (s.rfind("plan_", 0) == 0 && !h->plans.empty()) {  // plan of the most recent L
@@ -582,12 +611,50 @@ int coral_search_prepare(coral_index_t* h, int max_queries, int max_L, int max_k
     CK(cudaMalloc(&h->d_gcand, (size_t)h->grid_cap * h->cand_cap_alloc * sizeof(uint64_t)));
     CK(cudaMalloc(&h->d_cctl, (size_t)h->sm_count * sizeof(coral::ClusterCtl)));
     CK(cudaMalloc(&h->d_gexp, (size_t)h->sm_count * max_L * sizeof(int32_t)));
+    CK(cudaMalloc(&h->d_keys, (size_t)max_queries * sizeof(int)));
+    CK(cudaMalloc(&h->d_order, (size_t)max_queries * sizeof(int32_t)));
+    CK(cudaMalloc(&h->d_bins, (size_t)kMaxFrontier * sizeof(int)));
     CK(cudaMalloc(&h->d_queries, (size_t)max_queries * h->dim * sizeof(float)));
     CK(cudaMalloc(&h->d_ids, (size_t)max_queries * max_k * sizeof(int32_t)));
     CK(cudaMalloc(&h->d_dists, (size_t)max_queries * max_k * sizeof(float)));
     CK(cudaMalloc(&h->d_stats, (size_t)max_queries * CORAL_STATS_W * sizeof(int32_t)));
     CK(cudaStreamSynchronize(h->stream));
     h->prepared = true;
+    return CORAL_OK;
+}
+
+// The frontier of the first expansion round -- the distinct neighbours of the entry points -- as
+// a contiguous block of vectors for the scheduling pre-pass.  Rebuilt when vectors, graph or
+// entry points change.  Synchronises h->stream (set-up path, not the search path).
+static int ensure_frontier(coral_index* h) {
+    if (!h->frontier_dirty) return CORAL_OK;
+    h->frontier_dirty = false;
+    h->n_front = 0;
+    if (h->M > 64) return CORAL_OK;   // many entry points: the frontier would not be a cheap predictor
+    std::vector<int32_t> rows((size_t)h->M * h->deg_pad);
+    for (int i = 0; i < h->M; ++i)
+        CK(cudaMemcpy(rows.data() + (size_t)i * h->deg_pad, h->d_adj + (size_t)h->h_start[i] * h->deg_pad,
+                      (size_t)h->deg_pad * sizeof(int32_t), cudaMemcpyDeviceToHost));
+    std::sort(rows.begin(), rows.end());
+    rows.erase(std::unique(rows.begin(), rows.end()), rows.end());
+    std::vector<int32_t> ids;
+    for (int32_t v : rows)
+        if (v >= 0 && (int64_t)v < h->n && (int)ids.size() < kMaxFrontier) ids.push_back(v);
+    if (ids.size() < 2) return CORAL_OK;
+    cudaFree(h->d_front_ids);
+    cudaFree(h->d_front_vecs);
+    cudaFree(h->d_front_norm);
+    h->d_front_ids = nullptr;
+    h->d_front_vecs = h->d_front_norm = nullptr;
+    CK(cudaMalloc(&h->d_front_ids, ids.size() * sizeof(int32_t)));
+    CK(cudaMalloc(&h->d_front_vecs, ids.size() * (size_t)h->dim * sizeof(float)));
+    CK(cudaMalloc(&h->d_front_norm, ids.size() * sizeof(float)));
+    CK(cudaMemcpyAsync(h->d_front_ids, ids.data(), ids.size() * sizeof(int32_t), cudaMemcpyHostToDevice, h->stream));
+    CK(coral::gather_frontier(h->d_vecs, h->d_front_ids, (int)ids.size(), h->dim, h->d_front_vecs, h->d_front_norm,
+                              h->stream));
+    h->launches += 1;
+    CK(cudaStreamSynchronize(h->stream));
+    h->n_front = (int)ids.size();
     return CORAL_OK;
 }
 
@@ -664,6 +731,18 @@ static int enqueue_search(coral_index* h, const float* d_queries, int Q, int L, 
         }
     }
     h->last_cluster_size = cs;
+    // Large batches: run the queries grouped by their best frontier node (see schedule.cu).
+    h->last_scheduled = 0;
+    if (cs == 1 && h->opt.schedule >= 0 && (h->opt.schedule > 0 || Q >= 8192)) {
+        if (int rc = ensure_frontier(h)) return rc;
+        if (h->n_front >= 2) {
+            CK(coral::schedule_queries(d_queries, Q, h->dim, h->metric, h->d_front_vecs, h->d_front_norm, h->n_front,
+                                       h->d_keys, h->d_bins, h->d_order, h->sm_count, st));
+            h->launches += 4;
+            a.order = h->d_order;
+            h->last_scheduled = 1;
+        }
+    }
     CK(coral::launch_beam_search(a, h->metric, grid, st, cs));
     h->launches += 1;
     h->epoch_base += (uint32_t)Q;

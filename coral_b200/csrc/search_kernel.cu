@@ -357,7 +357,8 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                 q = group + turn * n_groups;   // static: every CTA of the cluster must agree
             else if (*(volatile int*)a.err_flag == 0)
                 q = atomicAdd(a.q_counter, 1);
-            if (q >= a.Q) q = -1;
+            if (q < 0 || q >= a.Q) q = -1;
+            else if (a.order) q = a.order[q];   // scheduled batches: the q-th query to run, results stay at its own row
             S.qid = q;
             S.status = 0;
             S.worst = METRIC == 0 ? 3.402823466e+38f : -3.402823466e+38f;

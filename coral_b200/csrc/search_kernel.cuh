@@ -48,6 +48,7 @@ struct SearchArgs {
     long long* dbg;            // self-checking build only: [0] first failed check, [1..4] its values
     ClusterCtl* cctl;          // cluster mode: [clusters] round state
     int32_t* gexp;             // cluster mode: [clusters][L] ids to expand this round
+    const int32_t* order;      // nullable: order[i] = the i-th query to run (locality scheduling)
     int64_t n;
     int dim, deg_pad, deg_shift, M, Q, L, k;
     uint32_t epoch_base;       // epoch of query q is epoch_base + q + 1 (never 0)

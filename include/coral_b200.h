@@ -131,7 +131,10 @@ int64_t coral_launch_count(coral_index_t* h);
  * global table), "ghash_factor", "ghash_entries", "max_rounds", "cluster_size" (CTAs that
  * share one query when the batch is far smaller than the GPU: 0 = automatic, 1 = never,
  * 2/4/8/16 = forced; results do not depend on it), "scout_ids" (neighbour ids a lane examines
- * per scout step, 1..4, 0 = automatic).  Returns CORAL_ERR_ARG for unknown names. */
+ * per scout step, 1..4, 0 = automatic), "schedule" (run large batches grouped by the entry
+ * points' neighbour each query is closest to, for L2 locality: 0 = automatic for batches
+ * >= 8192, 1 = always, -1 = never; results do not depend on it).  Returns CORAL_ERR_ARG for
+ * unknown names. */
 int coral_set_option(coral_index_t* h, const char* name, int value);
 int coral_get_option(coral_index_t* h, const char* name, int* value);
 

@@ -106,6 +106,23 @@ def test_tuning_knobs_do_not_change_results(opts):
         assert_same(c, ix, 256, 10)
 
 
+@pytest.mark.parametrize("metric", ["l2", "ip"])
+def test_locality_scheduling_changes_only_the_order_of_work(metric):
+    # Large batches are run grouped by their best "frontier" node (the entry points' neighbours);
+    # forced on here for a small batch.  Every query's result stays at its own row.
+    c = cases.structured(metric)
+    with make_index(c, len(c.queries), 128, 10, options={"schedule": 1}) as ix:
+        assert_same(c, ix, 64, 10, modes=(1,))
+        assert ix.get_option("last_scheduled") == 1 and ix.get_option("frontier_size") >= 2
+        assert_same(c, ix, 128, 10, queries=c.queries[:37], modes=(1,))     # ragged tile of the pre-pass
+    with make_index(c, len(c.queries), 64, 10, options={"schedule": -1}) as ix:
+        assert_same(c, ix, 64, 10, modes=(1,))
+        assert ix.get_option("last_scheduled") == 0
+    r = cases.random_case(metric, 3000, 36, 32, 50, m=3, seed=41)             # tiny frontier, odd dim
+    with make_index(r, 50, 64, 10, options={"schedule": 1}) as ix:
+        assert_same(r, ix, 64, 10, modes=(1,))
+
+
 def test_small_sort_tiles_take_many_fill_passes():
     # Tiny staging memory -> tiny candidate sort tiles -> a round's candidates need many
     # fill passes; every thread must agree on when a tile is full (barrier-counted).
