@@ -42,6 +42,8 @@ struct Options {
     int max_rounds = 1 << 16;
     int cluster_size = 0;  // CTAs sharing one query in small batches: 0 = automatic, 1 = never, else 2/4/8/16
     int scout_ids = 0;     // neighbour ids per lane per scout step: 0 = automatic (4; 1 in cluster mode), else 1..4
+    int visit_cache_bits = 0;  // shared-memory cache of recently seen ids in front of the visited table (log2 entries)
+    int sort_tile = 0;     // candidate sort tile in keys: 0 = automatic (about twice the beam capacity)
     int schedule = 0;      // order large batches for L2 locality: 0 = automatic (batches >= 8192), 1 = always, -1 = never
 };
 
@@ -178,6 +180,7 @@ bool make_plan_warps(const coral_index* h, int L, int warps, SearchPlan& p, std:
     p.stage_bytes = 32 * p.row_stride;
     p.LP = next_pow2(std::max(L, 32));
     p.hs_bits = std::min(std::max(o.smem_hash_bits, 0), 16);
+    p.vc_bits = std::min(std::max(o.visit_cache_bits, 0), 14);
 
     const int budget = h->smem_optin / p.ctas_per_sm - 1024;  // the runtime keeps 1 KB per CTA
     for (;;) {
@@ -187,6 +190,7 @@ bool make_plan_warps(const coral_index* h, int L, int warps, SearchPlan& p, std:
         p.off_beam1 = off;  off += p.LP * 8;
         p.off_exp = off;    off = align_up(off + L * 4, 16);
         p.off_hash = off;   off += p.hs_bits > 0 ? (4 << p.hs_bits) : 0;
+        p.off_vcache = off; off += p.vc_bits > 0 ? (4 << p.vc_bits) : 0;
         p.off_bar = off;    off += p.warps * 8 * 8;  // room for up to 8 stages
         p.off_pend = off;   off += p.warps * 160 * 4;
         p.off_bids = off;   off += p.warps * 64 * 4;
@@ -210,9 +214,16 @@ bool make_plan_warps(const coral_index* h, int L, int warps, SearchPlan& p, std:
         return false;
     }
     if (auto_ctas) p.ctas_per_sm = std::min(std::max(h->smem_optin / (p.smem_bytes + 1024), 1), 8);
+    // Candidate sort tile.  Only the L best of a round's candidates survive, and after each tile is
+    // merged the L-th key tightens the filter for the rest, so small tiles (about 2L) sort far
+    // fewer keys in total than one big tile: a round with 1500 candidates and L = 64 sorts ~300
+    // keys in 256-key tiles instead of 2048.  Bounded by the staging memory the tile lives in.
     int tile = 64;
-    const int cap = std::min(p.warps * p.stages * p.stage_bytes / 8, 2048);
+    int cap = std::min(p.warps * p.stages * p.stage_bytes / 8, 2048);
+    const int want = o.sort_tile > 0 ? o.sort_tile : std::max(2 * p.LP, next_pow2(p.warps * 32));
+    cap = std::min(cap, std::max(want, p.warps * 32));
     while (tile * 2 <= cap) tile <<= 1;
+    if (tile < p.warps * 32 && tile * 2 <= std::min(p.warps * p.stages * p.stage_bytes / 8, 2048)) tile <<= 1;
     p.tile_max = tile;
     if (p.tile_max < p.warps * 32) {
         why = "staging area too small to sort a candidate tile";
@@ -537,6 +548,8 @@ int coral_set_option(coral_index_t* h, const char* name, int value) {
     else if (s == "cluster_size") o.cluster_size = value;
     else if (s == "scout_ids") o.scout_ids = value;
     else if (s == "schedule") o.schedule = value;
+    else if (s == "sort_tile") o.sort_tile = value;
+    else if (s == "visit_cache_bits") o.visit_cache_bits = value;
     else return fail(h, CORAL_ERR_ARG, "unknown option " + s);
     h->plans.clear();
     return CORAL_OK;

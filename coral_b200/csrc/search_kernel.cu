@@ -92,12 +92,28 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
         : "memory");
     return ok;
 }
-// Bounded wait: returns false (and raises *err) when the limit ran out.
+// try_wait that lets the hardware park the thread for up to `ns` nanoseconds while the phase is
+// pending, instead of returning at once.
+__device__ __forceinline__ uint32_t mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok;
+}
+// Bounded wait: returns false (and raises *err) when the limit ran out.  A row chunk takes about
+// a microsecond to arrive and dozens of warps per SM wait at any time: a tight polling loop made
+// 80 % of all issued instructions (measured), starving the warps that had arithmetic to do.  So the
+// wait parks, and the clock limit is only looked at every 64 wake-ups.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > kWaitClocks) {
+    for (uint32_t spins = 1; !mbar_try_wait_parked(bar, parity, 4000u); ++spins) {
+        if ((spins & 63u) == 0u && clock64() - t0 > kWaitClocks) {
             atomicExch(err, 1);
             return false;
         }
@@ -308,6 +324,10 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
     uint64_t* beam_alt = reinterpret_cast<uint64_t*>(smem + P.off_beam1);
     int* exp_list = reinterpret_cast<int*>(smem + P.off_exp);
     uint32_t* shash = reinterpret_cast<uint32_t*>(smem + P.off_hash);
+    // Direct-mapped cache of ids this CTA has already put through the visited set: a hit means
+    // "seen" without touching the table (an entry is only written after the table answered).
+    uint32_t* vcache = reinterpret_cast<uint32_t*>(smem + P.off_vcache);
+    const uint32_t vc_mask = P.vc_bits > 0 ? (1u << P.vc_bits) - 1u : 0u;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P.off_bar) + warp * P.stages;
     int* pend = reinterpret_cast<int*>(smem + P.off_pend) + warp * kPendCap;
     int* bids = reinterpret_cast<int*>(smem + P.off_bids) + warp * 64;  // two batch slots of 32 ids
@@ -335,9 +355,14 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
     fence_async_smem();
     __syncthreads();
 
-    // chunk stream positions of this warp; monotonic over the kernel's life so
-    // that the parity of use u of a stage is u & 1.
-    uint32_t iss = 0, con = 0;
+    // This warp's stream of row chunks.  A batch (<= 32 rows) is n_chunks chunks; chunks go through
+    // the ring's stages round-robin.  All bookkeeping is incremental (no divisions in the loop) and
+    // lives for the whole kernel, so that the parity of the u-th use of a stage is u & 1.
+    uint32_t formed = 0, issued = 0, done = 0;   // batches formed / completely issued / finalised
+    int iss_c = 0, con_c = 0;                    // chunks of the current batch issued / consumed
+    int iss_st = 0, con_st = 0;                  // ring stage the next issue / consume uses
+    uint32_t con_par = 0;                        // parity the next consume waits for
+    int inflight = 0;                            // chunks issued and not yet consumed
     const int n_chunks = P.n_chunks;
     const int chunk_vec = P.chunk_bytes >> 4;
     const int chunk_floats = P.chunk_bytes >> 2;
@@ -374,6 +399,8 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
         for (int d = tid; d < a.dim; d += nthreads) sq[d] = a.queries[(size_t)qid * a.dim + d];
         if (P.hs_bits > 0)
             for (int i = tid; i < (1 << P.hs_bits); i += nthreads) shash[i] = kEmpty32;
+        if (P.vc_bits > 0)
+            for (int i = tid; i < (1 << P.vc_bits); i += nthreads) vcache[i] = kEmpty32;
         for (int i = tid; i < P.LP; i += nthreads) beam[i] = kPadKey;
         __syncthreads();
 
@@ -436,8 +463,6 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
             // ------------------------------------------------------------ warp pipeline
             {
                 int pend_n = 0;
-                uint32_t formed = iss / n_chunks;  // batches formed so far (== consumed here)
-                uint32_t done = formed;            // batches finalised
                 int bcnt0 = 0, bcnt1 = 0;          // rows in batch slot 0 / 1
                 bool more = exp_count > 0;
                 float acc = 0.f;
@@ -454,8 +479,9 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                         __syncwarp();
                     }
                     // keep the ring full
-                    while (iss < formed * (uint32_t)n_chunks && iss - con < (uint32_t)P.stages) {
-                        const uint32_t b = iss / n_chunks, c = iss - b * n_chunks, st = iss % P.stages;
+                    while (issued < formed && inflight < P.stages) {
+                        const uint32_t b = issued;
+                        const int c = iss_c, st = iss_st;
                         const int cnt = (b & 1u) ? bcnt1 : bcnt0;
                         if (lane == 0) mbar_expect_tx(&bars[st], (uint32_t)cnt * (uint32_t)P.chunk_bytes);
                         __syncwarp();
@@ -467,7 +493,12 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                                          (size_t)c * P.chunk_bytes,
                                      (uint32_t)P.chunk_bytes, &bars[st]);
                         }
-                        ++iss;
+                        ++inflight;
+                        iss_st = iss_st + 1 == P.stages ? 0 : iss_st + 1;
+                        if (++iss_c == n_chunks) {
+                            iss_c = 0;
+                            ++issued;
+                        }
                     }
                     if (more && pend_n < 32) {
                         // ---- scout: adjacency rows of up to G entries, visited test-and-set
@@ -501,10 +532,13 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                             isnew[t] = false;
                             if (v[t] >= 0 && (int64_t)v[t] < a.n) {
                                 ++n_scan;
+                                const uint32_t cslot = ((uint32_t)v[t] * 0x9E3779B1u >> 7) & vc_mask;
+                                if (P.vc_bits > 0 && vcache[cslot] == (uint32_t)v[t]) continue;   // seen before
                                 const int r =
                                     visited_insert(shash, P.hs_bits, ghash, a.gh_mask, epoch, v[t], n_spill);
                                 isnew[t] = (r == 0);
                                 if (r == 2) overflow = true;
+                                else if (P.vc_bits > 0) vcache[cslot] = (uint32_t)v[t];
                             }
                         }
 #pragma unroll
@@ -517,11 +551,12 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                         __syncwarp();
                         continue;
                     }
-                    if (con < iss) {
+                    if (inflight > 0) {
                         // ---- distance: one chunk of the oldest batch in flight
-                        const uint32_t b = con / n_chunks, c = con - b * n_chunks, st = con % P.stages;
+                        const uint32_t b = done;
+                        const int c = con_c, st = con_st;
                         const int cnt = (b & 1u) ? bcnt1 : bcnt0;
-                        mbar_wait(&bars[st], (con / P.stages) & 1u, a.err_flag);
+                        mbar_wait(&bars[st], con_par, a.err_flag);
                         if (c == 0) acc = 0.f;
                         if (lane < cnt)
                             acc = accumulate_chunk<METRIC>(
@@ -531,8 +566,13 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                                 reinterpret_cast<const float4*>(sq + (size_t)c * chunk_floats), chunk_vec);
                         fence_async_smem();
                         __syncwarp();
-                        ++con;
-                        if (c == (uint32_t)n_chunks - 1u) {
+                        --inflight;
+                        if (++con_st == P.stages) {
+                            con_st = 0;
+                            con_par ^= 1u;
+                        }
+                        if (++con_c == n_chunks) {
+                            con_c = 0;
                             // ---- filter and emit (src/search_gpu.cu:431-434)
                             const bool ok = lane < cnt && closer_than<METRIC>(worst, acc);
                             const uint32_t m = __ballot_sync(0xffffffffu, ok);

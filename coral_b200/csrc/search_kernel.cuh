@@ -15,10 +15,11 @@ struct SearchPlan {
     int row_stride;   // bytes between two rows inside a stage (padded against bank conflicts)
     int stage_bytes;  // 32 * row_stride
     int hs_bits;      // log2 entries of the shared-memory visited hash, 0 = none
+    int vc_bits;      // log2 entries of the shared-memory cache of recently seen ids, 0 = none
     int LP;           // beam array length: L rounded up to a power of two
     int tile_max;     // largest candidate tile sorted at once (power of two)
     int ctas_per_sm;
-    int off_query, off_beam0, off_beam1, off_exp, off_hash, off_bar, off_pend, off_bids, off_stage;
+    int off_query, off_beam0, off_beam1, off_exp, off_hash, off_vcache, off_bar, off_pend, off_bids, off_stage;
     int smem_bytes;
 };
 

@@ -98,6 +98,8 @@ def test_underfull_beam_is_reported_not_faulted():
     {"warps": 3, "ctas_per_sm": 1, "chunk_bytes": 2048},
     {"scout_ids": 1},                              # 32 neighbour slots per scout step (half an adjacency row)
     {"scout_ids": 3, "warps": 5},
+    {"visit_cache_bits": 9},                       # shared-memory cache of recently seen ids
+    {"visit_cache_bits": 3, "smem_hash_bits": 8},  # a cache that thrashes, in front of both tables
 ])
 def test_tuning_knobs_do_not_change_results(opts):
     c = cases.structured("ip")
