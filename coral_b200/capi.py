@@ -21,7 +21,8 @@ OK, ERR_ARG, ERR_STATE, ERR_CUDA, ERR_NOGPU, ERR_KERNEL, ERR_LIMIT = range(7)
 EXPORTS = (
     "coral_version", "coral_compiled_sm", "coral_index_create", "coral_index_destroy",
     "coral_index_set_vectors", "coral_index_attach_vectors", "coral_index_set_slots",
-    "coral_index_set_adjacency", "coral_index_set_start_ids", "coral_index_set_deleted",
+    "coral_index_set_adjacency", "coral_index_set_start_ids", "coral_index_select_start_ids",
+    "coral_index_set_deleted",
     "coral_search_prepare", "coral_search_free", "coral_search", "coral_search_async",
     "coral_search_check", "coral_last_kernel_ms", "coral_last_total_ms", "coral_launch_count",
     "coral_set_option", "coral_get_option", "coral_count_hits", "coral_merge_shards",
@@ -59,6 +60,7 @@ def load():
         "coral_index_set_slots": (C.c_int, [vp, i32p, C.c_size_t, i32p, C.c_size_t]),
         "coral_index_set_adjacency": (C.c_int, [vp, i32p, C.c_int]),
         "coral_index_set_start_ids": (C.c_int, [vp, i32p, C.c_int]),
+        "coral_index_select_start_ids": (C.c_int, [vp, C.c_int, C.c_int, i32p]),
         "coral_index_set_deleted": (C.c_int, [vp, vp]),
         "coral_search_prepare": (C.c_int, [vp, C.c_int, C.c_int, C.c_int]),
         "coral_search_free": (C.c_int, [vp]),
@@ -168,6 +170,14 @@ class Index:
     def set_start_ids(self, ids):
         a = np.ascontiguousarray(ids.cpu().numpy() if _is_torch(ids) else ids, dtype=np.int32)
         self._check(self._lib.coral_index_set_start_ids(self._h, C.c_void_p(a.ctypes.data), int(a.size)))
+
+    def select_start_ids(self, first_id, M):
+        """Farthest-point sampling of M entry points from `first_id` (the reference's Graph::FPS with a
+        caller-chosen first node); installs them and returns them as int32 [M]."""
+        out = np.empty(int(M), dtype=np.int32)
+        self._check(self._lib.coral_index_select_start_ids(self._h, int(first_id), int(M),
+                                                           C.c_void_p(out.ctypes.data)))
+        return out
 
     def set_deleted(self, bits):
         if bits is None:

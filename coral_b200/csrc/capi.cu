@@ -15,6 +15,7 @@
 #include "../../include/coral_b200.h"
 #include "schedule.cuh"
 #include "search_kernel.cuh"
+#include "start_select.cuh"
 
 using coral::SearchArgs;
 using coral::SearchPlan;
@@ -34,7 +35,7 @@ struct Options {
     // CTAs beats spending it on a shared-memory visited table.
     int ctas_per_sm = 0;  // 0 = as many as shared memory allows (at most 8)
     int warps = 0;        // 0 = 3..6, whichever keeps most warps resident per SM
-    int chunk_bytes = 256;
+    int chunk_bytes = 0;   // bytes of a row moved by one bulk copy: 0 = automatic (about 256, see make_plan)
     int stages = 0;  // 0 = one stage when ctas_per_sm is automatic, else as many as fit (at most 6)
     int smem_hash_bits = 0;
     int ghash_factor = 8;  // global visited table entries >= factor * L * deg_pad
@@ -44,6 +45,7 @@ struct Options {
     int scout_ids = 0;     // neighbour ids per lane per scout step: 0 = automatic (4; 1 in cluster mode), else 1..4
     int visit_cache_bits = 0;  // shared-memory cache of recently seen ids in front of the visited table (log2 entries)
     int sort_tile = 0;     // candidate sort tile in keys: 0 = automatic (about twice the beam capacity)
+    int gather = 0;        // row chunks to shared memory: 0 = one bulk copy per row chunk, 1 = 16-byte unit copies
     int schedule = 0;      // order large batches for L2 locality: 0 = automatic (batches >= 8192), 1 = always, -1 = never
 };
 
@@ -87,6 +89,7 @@ struct coral_index {
     int* d_bins = nullptr;
     int32_t* d_order = nullptr;
     int last_scheduled = 0;
+    int last_plan_key = -1;   // plans[] key of the most recent search or prepare
     size_t cand_cap_alloc = 0;
     float* d_queries = nullptr;
     int32_t* d_ids = nullptr;
@@ -139,7 +142,7 @@ int next_pow2(int x) {
 int align_up(int x, int a) { return (x + a - 1) / a * a; }
 
 // Shared-memory plan for beam capacity L; returns false when nothing fits.
-bool make_plan_warps(const coral_index* h, int L, int warps, SearchPlan& p, std::string& why);
+bool make_plan_warps(const coral_index* h, int L, int warps, SearchPlan& p, std::string& why, int chunk_target = 0);
 
 // With warps = 0 the warp count per CTA is chosen to maximise resident warps per SM
 // (CTAs per SM x warps), preferring more CTAs on a tie: on 10M x 512 the achieved bandwidth
@@ -157,17 +160,35 @@ bool make_plan(const coral_index* h, int L, SearchPlan& p, std::string& why) {
         found = true;
     }
     if (!found) return make_plan_warps(h, L, 4, p, why);
+    // Every bulk copy costs its warp about 54 cycles to issue whatever its size, so rows that do
+    // not split into 256-byte chunks (dim 200: five chunks of 160 bytes) are better moved in chunks
+    // of up to 512 bytes -- as long as five CTAs still fit an SM (measured on 1M x 200, L = 64:
+    // 1.85M against 1.56M queries/s with 400-byte chunks; at L = 512, where only four CTAs fit,
+    // 160-byte chunks stay ahead).
+    if (h->opt.chunk_bytes <= 0 && p.chunk_bytes < 256) {
+        SearchPlan best{};
+        bool have = false;
+        for (int w : {3, 4, 5, 6}) {
+            SearchPlan q;
+            std::string dummy;
+            if (!make_plan_warps(h, L, w, q, dummy, 512) || q.chunk_bytes <= p.chunk_bytes) continue;
+            const int total = q.ctas_per_sm * q.warps, cur = best.ctas_per_sm * best.warps;
+            if (!have || total > cur || (total == cur && q.ctas_per_sm > best.ctas_per_sm)) best = q;
+            have = true;
+        }
+        if (have && best.ctas_per_sm >= 5) p = best;
+    }
     return true;
 }
 
-bool make_plan_warps(const coral_index* h, int L, int warps, SearchPlan& p, std::string& why) {
+bool make_plan_warps(const coral_index* h, int L, int warps, SearchPlan& p, std::string& why, int chunk_target) {
     const Options& o = h->opt;
     const int row_bytes = h->dim * 4;
     p = SearchPlan{};
     p.warps = std::min(std::max(warps, 1), 16);
     const bool auto_ctas = o.ctas_per_sm <= 0;
     p.ctas_per_sm = auto_ctas ? 1 : std::min(o.ctas_per_sm, 8);
-    int target = std::max(16, o.chunk_bytes);
+    int target = std::max(16, chunk_target > 0 ? chunk_target : (o.chunk_bytes > 0 ? o.chunk_bytes : 256));
     int nc = (row_bytes + target - 1) / target;
     while (nc <= row_bytes / 16 && !(row_bytes % nc == 0 && (row_bytes / nc) % 16 == 0)) ++nc;
     if (nc > row_bytes / 16) {
@@ -181,6 +202,7 @@ bool make_plan_warps(const coral_index* h, int L, int warps, SearchPlan& p, std:
     p.LP = next_pow2(std::max(L, 32));
     p.hs_bits = std::min(std::max(o.smem_hash_bits, 0), 16);
     p.vc_bits = std::min(std::max(o.visit_cache_bits, 0), 14);
+    p.gather = o.gather == 1 ? 1 : 0;
 
     const int budget = h->smem_optin / p.ctas_per_sm - 1024;  // the runtime keeps 1 KB per CTA
     for (;;) {
@@ -192,7 +214,7 @@ bool make_plan_warps(const coral_index* h, int L, int warps, SearchPlan& p, std:
         p.off_hash = off;   off += p.hs_bits > 0 ? (4 << p.hs_bits) : 0;
         p.off_vcache = off; off += p.vc_bits > 0 ? (4 << p.vc_bits) : 0;
         p.off_bar = off;    off += p.warps * 8 * 8;  // room for up to 8 stages
-        p.off_pend = off;   off += p.warps * 160 * 4;
+        p.off_pend = off;   off += p.warps * coral::kPendCap * 4;
         p.off_bids = off;   off += p.warps * 64 * 4;
         off = align_up(off, 128);
         p.off_stage = off;
@@ -239,6 +261,7 @@ int get_plan(coral_index* h, int L, SearchPlan& p, int& per_sm, bool small_batch
     const bool tuned = h->opt.warps > 0 || h->opt.ctas_per_sm > 0;
     const int key = 2 * L + ((small_batch && !tuned) ? 1 : 0);
     auto it = h->plans.find(key);
+    h->last_plan_key = key;
     if (it != h->plans.end()) {
         p = it->second.first;
         per_sm = it->second.second;
@@ -518,6 +541,25 @@ int coral_index_set_start_ids(coral_index_t* h, const int32_t* ids, int M) {
     return CORAL_OK;
 }
 
+int coral_index_select_start_ids(coral_index_t* h, int first_id, int M, int32_t* ids_out) {
+    if (!h || M <= 0 || M > 4096) return fail(h, CORAL_ERR_ARG, "select start ids: need 1..4096 ids");
+    if (first_id < 0 || (int64_t)first_id >= h->n) return fail(h, CORAL_ERR_ARG, "first id out of range");
+    if (!h->d_adj) return fail(h, CORAL_ERR_STATE, "select start ids: no adjacency set");
+    if (int rc = ensure_device(h)) return rc;
+    std::vector<int32_t> row((size_t)h->deg_pad);
+    CK(cudaMemcpyAsync(row.data(), h->d_adj + (size_t)first_id * h->deg_pad, row.size() * sizeof(int32_t),
+                       cudaMemcpyDeviceToHost, h->stream));
+    CK(cudaStreamSynchronize(h->stream));
+    bool has_edge = false;
+    for (int32_t v : row) has_edge |= v >= 0 && (int64_t)v < h->n;
+    if (!has_edge) return fail(h, CORAL_ERR_ARG, "first id has no out-edges");
+    std::vector<int32_t> ids((size_t)M);
+    CK(coral::select_start_ids(h->d_adj, h->n, h->deg_pad, first_id, M, ids.data(), h->sm_count, h->stream,
+                               &h->launches));
+    if (ids_out) std::copy(ids.begin(), ids.end(), ids_out);
+    return coral_index_set_start_ids(h, ids.data(), M);
+}
+
 int coral_index_set_deleted(coral_index_t* h, const uint32_t* bits) {
     if (!h) return CORAL_ERR_ARG;
     if (int rc = ensure_device(h)) return rc;
@@ -550,6 +592,7 @@ int coral_set_option(coral_index_t* h, const char* name, int value) {
     else if (s == "schedule") o.schedule = value;
     else if (s == "sort_tile") o.sort_tile = value;
     else if (s == "visit_cache_bits") o.visit_cache_bits = value;
+    else if (s == "gather") o.gather = value;
     else return fail(h, CORAL_ERR_ARG, "unknown option " + s);
     h->plans.clear();
     return CORAL_OK;
@@ -570,18 +613,23 @@ int coral_get_option(coral_index_t* h, const char* name, int* value) {
     else if (s == "cluster_size") *value = o.cluster_size;
     else if (s == "last_cluster_size") *value = h->last_cluster_size;
     else if (s == "schedule") *value = o.schedule;
+    else if (s == "gather") *value = o.gather;
+    else if (s == "sort_tile") *value = o.sort_tile;
+    else if (s == "scout_ids") *value = o.scout_ids;
+    else if (s == "visit_cache_bits") *value = o.visit_cache_bits;
     else if (s == "last_scheduled") *value = h->last_scheduled;
     else if (s == "frontier_size") *value = h->n_front;
     else if (s == "grid_cap") *value = h->grid_cap;
     else if (s == "deg_pad") *value = h->deg_pad;
-    else if (s.rfind("plan_", 0) == 0 && !h->plans.empty()) {  // plan of the most recent L
-        const SearchPlan& p = h->plans.rbegin()->second.first;
+    else if (s.rfind("plan_", 0) == 0 && h->plans.count(h->last_plan_key)) {  // plan of the most recent search
+        const auto& entry = h->plans[h->last_plan_key];
+        const SearchPlan& p = entry.first;
         if (s == "plan_stages") *value = p.stages;
         else if (s == "plan_warps") *value = p.warps;
         else if (s == "plan_chunk_bytes") *value = p.chunk_bytes;
         else if (s == "plan_smem_bytes") *value = p.smem_bytes;
         else if (s == "plan_hash_bits") *value = p.hs_bits;
-        else if (s == "plan_ctas_per_sm") *value = h->plans.rbegin()->second.second;
+        else if (s == "plan_ctas_per_sm") *value = entry.second;
         else return fail(h, CORAL_ERR_ARG, "unknown option " + s);
     } else return fail(h, CORAL_ERR_ARG, "unknown option " + s);
     return CORAL_OK;

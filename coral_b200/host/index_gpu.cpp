@@ -87,7 +87,25 @@ void IndexGPU::RunPrepare(Parameters& parameters, Mode mode, size_t n_bp, float*
     const coral_host::Adjacency g = coral_host::graph_dir_load(graph_dir, (int64_t)nd_, max_degree_);
     upload_graph(g.rows, g.deg_pad);
     start_ids_ = coral_host::start_ids_load(graph_dir + "/graph.search_start_ids");
-    if (start_ids_.empty()) throw std::runtime_error("no entry points in " + graph_dir + "/graph.search_start_ids");
+    if (start_ids_.empty()) {
+        // No saved entry points: choose them as Graph::get_search_start_nodes_fps does
+        // (src/graph.cpp:298-313 -> src/start.cu:72-145), starting from the lowest-numbered node that
+        // has an out-edge instead of a random one, and save them where the reference does
+        // (src/graph.cpp:315-327).
+        int first = -1;
+        for (int64_t i = 0; i < g.n && first < 0; ++i)
+            if (g.rows[(size_t)i * g.deg_pad] >= 0) first = (int)i;
+        if (first < 0) throw std::runtime_error("no entry points and no edges in " + graph_dir);
+        const int M = std::max(1, PC.search_start_nodes_num);
+        start_ids_.resize((size_t)M);
+        check(coral_index_select_start_ids(handle_, first, M, start_ids_.data()), "coral_index_select_start_ids");
+        try {
+            coral_host::start_ids_write(graph_dir + "/graph.search_start_ids", start_ids_);
+        } catch (const std::exception&) {
+            // a read-only graph directory: the reference only logs the failed write (src/graph.cpp:317-319)
+        }
+        return;
+    }
     check(coral_index_set_start_ids(handle_, start_ids_.data(), (int)start_ids_.size()), "coral_index_set_start_ids");
 }
 

@@ -86,6 +86,18 @@ int coral_index_set_adjacency(coral_index_t* h, const int32_t* adj, int deg_pad)
  * (src/search_gpu.cu:392-407). */
 int coral_index_set_start_ids(coral_index_t* h, const int32_t* ids, int M);
 
+/* Replaces Graph::FPS (src/start.cu:72-145): picks M entry points by
+ * farthest-point sampling over BFS hop counts on the installed adjacency and
+ * installs them as with coral_index_set_start_ids.  ids[0] = first_id; each
+ * further id is the lowest-numbered node whose smallest hop count from the
+ * ids chosen so far is largest (a node no chosen id reaches counts as -1).
+ * The reference draws the first node at random until it has an out-edge
+ * (src/start.cu:77-86); here the caller names it, so the same graph gives the
+ * same ids, and a first_id without out-edges is CORAL_ERR_ARG.  ids_out
+ * (host, M ints) may be NULL.  Needs 16 bytes of device scratch per node,
+ * freed before returning. */
+int coral_index_select_start_ids(coral_index_t* h, int first_id, int M, int32_t* ids_out);
+
 /* Replaces d_deleted (src/search_gpu.cu:582-833, :716): bit i set = node i is
  * skipped when the final top-k is written.  Host pointer to (n+31)/32 words, or
  * NULL to clear. */

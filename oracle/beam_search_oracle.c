@@ -309,3 +309,59 @@ double coral_oracle_recall(const int32_t* res, const int32_t* gt, int Q, int k, 
         }
     return Q > 0 ? (double)hit / ((double)k * Q) : 0.0;
 }
+
+/* Entry-point selection: farthest-point sampling over BFS hop counts, restating
+ * Graph::FPS (src/start.cu:72-145) with its helpers bfs (:53-70), bfs_expand_kernel
+ * (:31-51), update_min_hop_kernel (:20-29) and the ArgMax at :122-126.  The reference draws
+ * the first node from std::random_device (:77-86); here the caller names it (`first`, which
+ * must have out-degree > 0 like the reference insists), so the result is reproducible.
+ * min_hops starts at INT_MAX; after every BFS a node keeps the smallest hop count seen, a
+ * node never reached yet becomes -1, and the next start is the FIRST index holding the
+ * largest min_hops (CUB ArgMax returns the lowest index among equals).
+ * Returns the number of ids written (== M), or -1 on bad arguments. */
+int coral_oracle_select_start_ids(const int32_t* adj, int64_t n, int deg_pad, int first, int M, int32_t* out) {
+    if (!adj || !out || n <= 0 || deg_pad <= 0 || M <= 0 || first < 0 || first >= n) return -1;
+    int* hops = (int*)malloc(sizeof(int) * (size_t)n);
+    int* min_hops = (int*)malloc(sizeof(int) * (size_t)n);
+    int* queue = (int*)malloc(sizeof(int) * (size_t)n);
+    for (int64_t i = 0; i < n; ++i) min_hops[i] = 2147483647;
+    int start = first, count = 0;
+    out[count++] = start;
+    while (count < M) {
+        for (int64_t i = 0; i < n; ++i) hops[i] = -1;
+        int head = 0, tail = 0;
+        hops[start] = 0;
+        queue[tail++] = start;
+        while (head < tail) { /* level-synchronous BFS == FIFO BFS for hop counts */
+            int u = queue[head++];
+            const int32_t* nb = adj + (size_t)u * deg_pad;
+            for (int j = 0; j < deg_pad; ++j) {
+                int v = nb[j];
+                if (v < 0 || v >= n) continue;
+                if (hops[v] == -1) {
+                    hops[v] = hops[u] + 1;
+                    queue[tail++] = v;
+                }
+            }
+        }
+        int best = -2147483647 - 1, best_i = 0;
+        for (int64_t i = 0; i < n; ++i) {
+            int h = hops[i];
+            if (h >= 0) {
+                if (h < min_hops[i] || min_hops[i] < 0) min_hops[i] = h;
+            } else if (min_hops[i] == 2147483647) {
+                min_hops[i] = -1;
+            }
+            if (min_hops[i] > best) {
+                best = min_hops[i];
+                best_i = (int)i;
+            }
+        }
+        start = best_i;
+        out[count++] = start;
+    }
+    free(hops);
+    free(min_hops);
+    free(queue);
+    return count;
+}

@@ -47,6 +47,8 @@ def _load():
         _lib.coral_oracle_dist_tree.argtypes = [f32p, f32p, C.c_int, C.c_int]
         _lib.coral_oracle_merge_shards.restype = C.c_int
         _lib.coral_oracle_merge_shards.argtypes = [i32p, f32p, C.c_int, C.c_int, C.c_int, C.c_int, i32p, f32p]
+        _lib.coral_oracle_select_start_ids.restype = C.c_int
+        _lib.coral_oracle_select_start_ids.argtypes = [i32p, C.c_int64, C.c_int, C.c_int, C.c_int, i32p]
         _lib.coral_oracle_recall.restype = C.c_double
         _lib.coral_oracle_recall.argtypes = [i32p, i32p, C.c_int, C.c_int, C.c_int]
         _set_cpu_sig(_lib)
@@ -133,6 +135,18 @@ def merge_shards(ids, dists, metric):
     if rc != 0:
         raise ValueError("coral_oracle_merge_shards: bad arguments")
     return oi, od
+
+
+def select_start_ids(adj, first, M):
+    """Farthest-point sampling over BFS hop counts from `first`; returns int32 [M]."""
+    lib = _load()
+    adj, ap = _i32(adj)
+    out = np.empty(M, dtype=np.int32)
+    rc = lib.coral_oracle_select_start_ids(ap, adj.shape[0], adj.shape[1], int(first), int(M),
+                                           out.ctypes.data_as(C.POINTER(C.c_int32)))
+    if rc != M:
+        raise ValueError("coral_oracle_select_start_ids rejected its arguments")
+    return out
 
 
 def recall(res, gt, k):

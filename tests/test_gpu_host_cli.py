@@ -71,3 +71,34 @@ def test_driver_reports_errors_instead_of_crashing(tmp_path):
     assert r.returncode != 0 and "cannot" in (r.stdout + r.stderr).lower()
     r = subprocess.run([exe, "--dist", "l2"], capture_output=True, text=True)
     assert r.returncode != 0 and "required" in r.stderr
+
+
+def test_driver_selects_and_saves_entry_points_when_none_are_stored(tmp_path):
+    """A graph directory without graph.search_start_ids: the mirror picks the entry points by
+    farthest-point sampling from the lowest-numbered node with an out-edge, saves them in the
+    reference's text form, and searches from them."""
+    build_host.build()
+    c = cases.structured("l2")
+    k = 10
+    (tmp_path / "base.fbin").write_bytes(struct.pack("<ii", c.n, c.dim) + c.base.tobytes())
+    (tmp_path / "query.fbin").write_bytes(struct.pack("<ii", len(c.queries), c.dim) + c.queries.tobytes())
+    gt = np.zeros((len(c.queries), 100), np.int32)
+    (tmp_path / "gt.bin").write_bytes(struct.pack("<ii", gt.shape[0], gt.shape[1]) + gt.tobytes())
+    degs = (c.adj >= 0).sum(1)
+    write_reference_graph_dir(str(tmp_path / "graph"), degs, c.adj, _literal_block)
+    (tmp_path / "config.json").write_text('{"dim": %d, "k": 100, "search_start_nodes_num": 12}' % c.dim)
+    exe = os.path.join(os.path.dirname(build_host.HOST_LIB), "test_search_pipeline")
+    cmd = [exe, "--dataset", "synthetic", "--data_type", "float", "--dist", "l2",
+           "--base_data_path", str(tmp_path / "base.fbin"), "--query_path", str(tmp_path / "query.fbin"),
+           "--gt_path", str(tmp_path / "gt.bin"), "--graph_path", str(tmp_path / "graph"),
+           "--config_file", str(tmp_path / "config.json"), "--max_degree", "32", "--k", str(k),
+           "--L", "64", "-T", "8", "--ids_out", str(tmp_path / "ids.bin")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    first = int(np.flatnonzero(degs > 0)[0])
+    want = oracle.select_start_ids(c.adj, first, 12)
+    saved = [int(x) for x in (tmp_path / "graph" / "graph.search_start_ids").read_text().split()]
+    assert saved == [12] + want.tolist()
+    ids = np.fromfile(tmp_path / "ids.bin", dtype=np.int32).reshape(len(c.queries), k)
+    ref_ids, _, _ = oracle.search(c.base, c.adj, want, c.queries, 64, k, "l2")
+    assert np.array_equal(ids, ref_ids)
