@@ -51,8 +51,8 @@ PEAK_FALLBACK_GBS = 6650.0
 # DRAM bytes moved by one full-size launch, from the single-pass ncu capture recorded in
 # profiles/ (workload, L) -> bytes; absent -> null in the JSON line.
 MEASURED_TRAFFIC = {
-    ("c3", 64): 1.026e12,      # dram__bytes_read 1.00 TB + dram__bytes_write 25.9 GB for 100k queries
-    ("small", 64): 3.369e10,   # 32.29 GB + 1.40 GB for 8192 queries
+    ("c3", 64): 3.771e11,      # dram__bytes_read 351.4 GB + dram__bytes_write 25.7 GB for 100k queries (locality-scheduled)
+    ("small", 64): 1.131e10,   # 9.94 GB + 1.37 GB for 8192 queries
 }
 
 

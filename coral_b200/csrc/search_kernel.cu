@@ -32,7 +32,7 @@ namespace coral {
 
 namespace {
 
-constexpr int kPendCap = 160;   // new ids waiting for a gather batch: < 32 left over + 128 per scout step
+constexpr int kScoutAhead = 64; // a scout step may start while fewer than this many ids are waiting
 constexpr int kIdsPerLane = 4;  // neighbour ids examined per lane per scout step
 constexpr int kSmemProbes = 8;
 constexpr int kGlobalProbes = 256;
@@ -126,6 +126,24 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                  "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+// 16-byte asynchronous copy global -> shared through the load/store path (L2 only, no L1
+// allocation); completion is tracked per thread in commit groups.
+__device__ __forceinline__ void ldgsts16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(__cvta_generic_to_global(src))
+                 : "memory");
+}
+__device__ __forceinline__ void ldgsts_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Waits until at most `younger` of this thread's commit groups are still pending.
+__device__ __forceinline__ void ldgsts_wait(int younger) {
+    switch (younger) {
+        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+        case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+        case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+        default: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    }
+}
 __device__ __forceinline__ void fence_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -197,7 +215,7 @@ __device__ __forceinline__ int visited_insert(uint32_t* sh, int hs_bits, uint64_
         }
     }
     const uint64_t mine = ((uint64_t)epoch << 32) | (uint32_t)id;
-    const uint32_t h = mix32((uint32_t)id);
+    const uint32_t h = mix32((uint32_t)id) & ~1u;   // probe sequences start on an aligned slot pair (see the scout step)
 #pragma unroll 1
     for (int p = 0; p < kGlobalProbes; ++p) {
         unsigned long long* slot = (unsigned long long*)&gh[(h + p) & gmask];
@@ -310,7 +328,7 @@ __device__ __forceinline__ float seed_distance(const float* __restrict__ row, co
 // merges; every CTA runs the scout/gather/distance pipeline against the shared global visited
 // table, work counter and candidate buffer; two cluster barriers per round.
 template <int METRIC, bool CLUSTER>
-__global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
+__global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ Control S;
 
@@ -372,6 +390,12 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
     const int ipl = a.ids_per_lane < 1 ? kIdsPerLane : (a.ids_per_lane > kIdsPerLane ? kIdsPerLane : a.ids_per_lane);
     const int step_slots = 32 * ipl;
     const int row_bytes = a.dim * 4;
+    // Unit-copy gather (P.gather == 1): a row chunk is chunk_vec 16-byte units; the warp's lanes
+    // walk the (row, unit) pairs of a stage 32 at a time, so one instruction copies whole
+    // contiguous runs (two 256-byte chunks, one 512-byte chunk, ...).
+    const bool unit_gather = P.gather == 1;
+    const int lane_r0 = lane / chunk_vec, lane_u0 = lane % chunk_vec;
+    const int step_r = 32 / chunk_vec, step_u = 32 % chunk_vec;
 
     for (int turn = 0;; ++turn) {
         // ---------------------------------------------------------------- take a query
@@ -466,9 +490,21 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                 int bcnt0 = 0, bcnt1 = 0;          // rows in batch slot 0 / 1
                 bool more = exp_count > 0;
                 float acc = 0.f;
+                // A scout step is split in two: its compare-and-swaps are issued and the warp goes back to
+                // gathering and distances; their answers (which take microseconds under load) are only
+                // looked at when the warp runs short of ids.
+                bool sc_pending = false;
+                uint32_t sc_cas = 0u;              // bit t: a compare-and-swap is in flight for sv[t]
+                int sv[kIdsPerLane];
+                unsigned long long scur[kIdsPerLane], sold[kIdsPerLane];
+#pragma unroll
+                for (int t = 0; t < kIdsPerLane; ++t) {
+                    sv[t] = -1;
+                    scur[t] = sold[t] = 0ull;
+                }
                 for (;;) {
                     // form gather batches from pending ids
-                    while (formed - done < 2u && (pend_n >= 32 || (!more && pend_n > 0))) {
+                    while (formed - done < 2u && (pend_n >= 32 || (!more && !sc_pending && pend_n > 0))) {
                         const int m = pend_n < 32 ? pend_n : 32;
                         const int slot = formed & 1u;
                         if (lane < m && CORAL_CHECK(pend_n - m + lane >= 0 && pend_n - m + lane < kPendCap, 2, pend_n, m))
@@ -483,6 +519,25 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                         const uint32_t b = issued;
                         const int c = iss_c, st = iss_st;
                         const int cnt = (b & 1u) ? bcnt1 : bcnt0;
+                        if (unit_gather) {
+                            const int* ids = bids + (b & 1u) * 32;
+                            unsigned char* dst0 = stage0 + (size_t)st * P.stage_bytes;
+                            const unsigned char* src0 =
+                                reinterpret_cast<const unsigned char*>(a.vecs) + (size_t)c * P.chunk_bytes;
+                            int r = lane_r0, u = lane_u0;
+                            while (r < cnt) {
+                                int id = ids[r];
+                                if (!CORAL_CHECK(id >= 0 && (int64_t)id < a.n && cnt <= 32 && (int)st < P.stages, 3, id, cnt)) id = 0;
+                                ldgsts16(dst0 + r * P.row_stride + u * 16, src0 + (size_t)id * row_bytes + u * 16);
+                                r += step_r;
+                                u += step_u;
+                                if (u >= chunk_vec) {
+                                    u -= chunk_vec;
+                                    ++r;
+                                }
+                            }
+                            ldgsts_commit();
+                        } else {
                         if (lane == 0) mbar_expect_tx(&bars[st], (uint32_t)cnt * (uint32_t)P.chunk_bytes);
                         __syncwarp();
                         if (lane < cnt) {
@@ -493,6 +548,7 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                                          (size_t)c * P.chunk_bytes,
                                      (uint32_t)P.chunk_bytes, &bars[st]);
                         }
+                        }
                         ++inflight;
                         iss_st = iss_st + 1 == P.stages ? 0 : iss_st + 1;
                         if (++iss_c == n_chunks) {
@@ -500,8 +556,45 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                             ++issued;
                         }
                     }
-                    if (more && pend_n < 32) {
-                        // ---- scout: adjacency rows of up to G entries, visited test-and-set
+                    if (sc_pending && pend_n < 32 && formed - done < 2u) {
+                        // ---- scout, second half: read the answers, settle what the first slot left open
+                        bool isnew[kIdsPerLane];
+#pragma unroll
+                        for (int t = 0; t < kIdsPerLane; ++t) {
+                            isnew[t] = false;
+                            // Keeps the comparison below from being scheduled next to the compare-and-swap
+                            // (where it would wait for the answer the first half was written to not wait for).
+                            asm volatile("" : "+l"(scur[t]));
+                            if (sv[t] >= 0) {
+                                int r = 3;   // 0 new, 1 seen, 2 table full, 3 = the first slot did not settle it
+                                if ((sc_cas >> t) & 1u) {
+                                    if (sold[t] == scur[t]) {
+                                        r = 0;
+                                        ++n_spill;
+                                    } else if (sold[t] == (((unsigned long long)epoch << 32) | (uint32_t)sv[t])) {
+                                        r = 1;   // the same id won the slot first (another lane or warp)
+                                    }
+                                } else if ((uint32_t)scur[t] == (uint32_t)sv[t]) {
+                                    r = 1;   // the slot held this id with this query's epoch
+                                }
+                                if (r == 3) r = visited_insert(shash, 0, ghash, a.gh_mask, epoch, sv[t], n_spill);
+                                isnew[t] = r == 0;
+                                if (r == 2) overflow = true;
+                            }
+                        }
+#pragma unroll
+                        for (int t = 0; t < kIdsPerLane; ++t) {
+                            const uint32_t m = __ballot_sync(0xffffffffu, isnew[t]);
+                            if (isnew[t] && CORAL_CHECK(pend_n + __popc(m & lt_mask) < kPendCap, 5, pend_n, m))
+                                pend[pend_n + __popc(m & lt_mask)] = sv[t];
+                            pend_n += __popc(m);
+                        }
+                        sc_pending = false;
+                        __syncwarp();
+                        continue;
+                    }
+                    if (more && !sc_pending && pend_n < kScoutAhead) {
+                        // ---- scout, first half: adjacency rows of the next slots, visited-table probes
                         int s0 = 0;
                         if (lane == 0) s0 = atomicAdd(p_exp_next, step_slots);
                         s0 = __shfl_sync(0xffffffffu, s0, 0);
@@ -525,6 +618,55 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                                 if (CORAL_CHECK(ent < a.L && node >= 0 && (int64_t)node < a.n, 4, node, ent))
                                     v[t] = __ldg(a.adj + (size_t)node * a.deg_pad + (slot & (a.deg_pad - 1)));
                             }
+                        }
+                        if (P.hs_bits == 0 && P.vc_bits == 0) {
+                            // Visited set entirely in the global table.  The first probe slots of a lane's
+                            // ids are loaded side by side; a slot of another query (or never used) is
+                            // claimed by compare-and-swap, whose answer is read in the second half.
+                            // The probe sequence of an id starts on an aligned pair of slots, read with
+                            // one 16-byte load: only when both hold other ids of this query (rare at the
+                            // table's load) is the id left to the full probe in the second half.
+                            unsigned long long* slot[kIdsPerLane];
+                            ulonglong2 pair[kIdsPerLane];
+#pragma unroll
+                            for (int t = 0; t < kIdsPerLane; ++t) {
+                                sv[t] = -1;
+                                slot[t] = nullptr;
+                                pair[t] = make_ulonglong2(0ull, 0ull);
+                                if (v[t] >= 0 && (int64_t)v[t] < a.n) {
+                                    ++n_scan;
+                                    sv[t] = v[t];
+                                    slot[t] = (unsigned long long*)&ghash[mix32((uint32_t)v[t]) & a.gh_mask & ~1u];
+                                    asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];"
+                                                 : "=l"(pair[t].x), "=l"(pair[t].y)
+                                                 : "l"(slot[t])
+                                                 : "memory");
+                                }
+                            }
+                            sc_cas = 0u;
+#pragma unroll
+                            for (int t = 0; t < kIdsPerLane; ++t) {
+                                scur[t] = ~0ull;   // "not settled by the pair": the full probe decides later
+                                if (sv[t] >= 0) {
+                                    const bool mine0 = (uint32_t)(pair[t].x >> 32) == epoch;
+                                    const bool mine1 = (uint32_t)(pair[t].y >> 32) == epoch;
+                                    if (mine0 && (uint32_t)pair[t].x == (uint32_t)sv[t]) {
+                                        scur[t] = pair[t].x;                       // seen
+                                    } else if (!mine0) {
+                                        scur[t] = pair[t].x;                       // first slot is free: claim it
+                                        sold[t] = atomicCAS(slot[t], scur[t], ((unsigned long long)epoch << 32) | (uint32_t)sv[t]);
+                                        sc_cas |= 1u << t;
+                                    } else if (mine1 && (uint32_t)pair[t].y == (uint32_t)sv[t]) {
+                                        scur[t] = pair[t].y;                       // seen, in the second slot
+                                    } else if (!mine1) {
+                                        scur[t] = pair[t].y;                       // second slot is free: claim it
+                                        sold[t] = atomicCAS(slot[t] + 1, scur[t], ((unsigned long long)epoch << 32) | (uint32_t)sv[t]);
+                                        sc_cas |= 1u << t;
+                                    }
+                                }
+                            }
+                            sc_pending = true;
+                            continue;
                         }
                         bool isnew[kIdsPerLane];
 #pragma unroll
@@ -556,7 +698,12 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                         const uint32_t b = done;
                         const int c = con_c, st = con_st;
                         const int cnt = (b & 1u) ? bcnt1 : bcnt0;
-                        mbar_wait(&bars[st], con_par, a.err_flag);
+                        if (unit_gather) {
+                            ldgsts_wait(inflight - 1);
+                            __syncwarp();   // every lane's units have landed and are visible to the warp
+                        } else {
+                            mbar_wait(&bars[st], con_par, a.err_flag);
+                        }
                         if (c == 0) acc = 0.f;
                         if (lane < cnt)
                             acc = accumulate_chunk<METRIC>(
@@ -592,7 +739,7 @@ __global__ void __launch_bounds__(512) beam_search_kernel(const SearchArgs a) {
                         }
                         continue;
                     }
-                    if (!more && pend_n == 0) break;
+                    if (!more && !sc_pending && pend_n == 0) break;
                 }
             }
             if (CLUSTER) {

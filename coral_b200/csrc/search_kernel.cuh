@@ -5,6 +5,10 @@
 
 namespace coral {
 
+// Per-warp list of new ids waiting for a gather batch (ints): fewer than 64 left over when a scout
+// step starts + up to 128 from the step, rounded up.  off_pend must reserve this much per warp.
+constexpr int kPendCap = 224;
+
 // Shared-memory plan of one CTA, computed on the host for (dim, L, deg_pad) and
 // the tuning knobs; every offset is in bytes from the start of dynamic smem.
 struct SearchPlan {
@@ -19,6 +23,7 @@ struct SearchPlan {
     int LP;           // beam array length: L rounded up to a power of two
     int tile_max;     // largest candidate tile sorted at once (power of two)
     int ctas_per_sm;
+    int gather;       // how row chunks reach shared memory: 0 = one bulk copy per row chunk, 1 = 16-byte unit copies
     int off_query, off_beam0, off_beam1, off_exp, off_hash, off_vcache, off_bar, off_pend, off_bids, off_stage;
     int smem_bytes;
 };

@@ -81,7 +81,7 @@ bool plan_for(int dim, int L, int smem_optin, coral::SearchPlan& p) {
     p.off_exp = off;    off = align_up(off + L * 4, 16);
     p.off_hash = off;
     p.off_bar = off;    off += p.warps * 8 * 8;
-    p.off_pend = off;   off += p.warps * 160 * 4;
+    p.off_pend = off;   off += p.warps * coral::kPendCap * 4;
     p.off_bids = off;   off += p.warps * 64 * 4;
     off = align_up(off, 128);
     p.off_stage = off;

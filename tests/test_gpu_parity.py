@@ -100,6 +100,11 @@ def test_underfull_beam_is_reported_not_faulted():
     {"scout_ids": 3, "warps": 5},
     {"visit_cache_bits": 9},                       # shared-memory cache of recently seen ids
     {"visit_cache_bits": 3, "smem_hash_bits": 8},  # a cache that thrashes, in front of both tables
+    {"gather": 0},                                 # one bulk copy per row chunk
+    {"gather": 1},                                 # 16-byte unit copies, one commit group per chunk
+    {"gather": 1, "stages": 3, "chunk_bytes": 128, "warps": 3},
+    {"gather": 1, "chunk_bytes": 1024, "warps": 2, "ctas_per_sm": 1},   # more units per chunk than lanes
+    {"gather": 0, "stages": 2},
 ])
 def test_tuning_knobs_do_not_change_results(opts):
     c = cases.structured("ip")
