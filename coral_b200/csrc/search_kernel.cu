@@ -6,8 +6,12 @@
 //
 //   scout    read the adjacency rows of beam entries still to be expanded
 //            (coalesced, 128 neighbour ids per step), test-and-set each id in
-//            the exact visited set (shared-memory hash, spilling to an
-//            epoch-tagged global table), keep the new ids;
+//            the exact visited set (an epoch-tagged global table; optionally a
+//            shared-memory hash in front of it), keep the new ids.  The step is
+//            split in two: the first half loads the first pair of probe slots
+//            of every id and issues the compare-and-swaps, the second half reads
+//            their answers only when the warp runs short of ids, so the
+//            microseconds an atomic takes under load overlap with gathering;
 //   gather   for 32 new ids at a time, bring the rows into shared memory chunk
 //            by chunk with one bulk asynchronous copy (cp.async.bulk, completion
 //            counted on an mbarrier) per row chunk, several stages in flight;
@@ -105,10 +109,10 @@ __device__ __forceinline__ uint32_t mbar_try_wait_parked(uint64_t* bar, uint32_t
         : "memory");
     return ok;
 }
-// Bounded wait: returns false (and raises *err) when the limit ran out.  A row chunk takes about
-// a microsecond to arrive and dozens of warps per SM wait at any time: a tight polling loop made
-// 80 % of all issued instructions (measured), starving the warps that had arithmetic to do.  So the
-// wait parks, and the clock limit is only looked at every 64 wake-ups.
+// Bounded wait: returns false (and raises *err) when the limit ran out.  Issuing a stage's 32 bulk
+// copies already takes the warp about 2000 cycles, so the first try usually succeeds (measured:
+// 0.0 retries per chunk on 10M x 512); when it does not, the retry parks the warp instead of
+// polling, and the clock limit is only looked at every 64 wake-ups.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();

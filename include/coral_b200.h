@@ -138,15 +138,32 @@ float coral_last_total_ms(coral_index_t* h);
 /* Number of kernels this library launched on behalf of the handle so far. */
 int64_t coral_launch_count(coral_index_t* h);
 
-/* Tuning knobs (before coral_search_prepare): "ctas_per_sm", "warps",
- * "chunk_bytes", "stages", "smem_hash_bits" (0 = visited set entirely in the
- * global table), "ghash_factor", "ghash_entries", "max_rounds", "cluster_size" (CTAs that
- * share one query when the batch is far smaller than the GPU: 0 = automatic, 1 = never,
- * 2/4/8/16 = forced; results do not depend on it), "scout_ids" (neighbour ids a lane examines
- * per scout step, 1..4, 0 = automatic), "schedule" (run large batches grouped by the entry
- * points' neighbour each query is closest to, for L2 locality: 0 = automatic for batches
- * >= 8192, 1 = always, -1 = never; results do not depend on it).  Returns CORAL_ERR_ARG for
- * unknown names. */
+/* Tuning knobs (set before coral_search_prepare; none of them changes a result):
+ *   "ctas_per_sm", "warps"   resident CTAs per SM and warps per CTA; 0 = automatic (the warps in
+ *                            3..6 that keep most warps resident; 8 warps for batches <= 4 x SMs)
+ *   "chunk_bytes"            bytes of a row moved by one bulk copy; 0 = automatic (256, or up to
+ *                            512 when the row does not split into 256-byte chunks and five CTAs
+ *                            still fit an SM)
+ *   "stages"                 stage buffers per warp; 0 = automatic (1)
+ *   "gather"                 0 = one bulk copy per row chunk (default), 1 = 16-byte cp.async units
+ *   "smem_hash_bits"         log2 entries of a shared-memory visited table in front of the global
+ *                            one; 0 = none (default)
+ *   "visit_cache_bits"       log2 entries of a shared-memory cache of recently seen ids; 0 = none
+ *   "ghash_factor", "ghash_entries"   global visited table per CTA: >= factor x L x deg_pad
+ *                            entries (default 8), or an explicit power of two >= 64
+ *   "sort_tile"              candidate keys sorted at once at the end of a round; 0 = automatic
+ *                            (about twice the beam capacity)
+ *   "scout_ids"              neighbour ids a lane examines per scout step, 1..4; 0 = automatic
+ *   "max_rounds"             per-query round limit (status 3 when reached)
+ *   "cluster_size"           CTAs that share one query when the batch is far smaller than the GPU:
+ *                            0 = automatic, 1 = never, 2/4/8/16 = forced
+ *   "schedule"               run large batches grouped by the entry points' neighbour each query is
+ *                            closest to, for L2 locality: 0 = automatic for batches >= 8192,
+ *                            1 = always, -1 = never
+ * coral_get_option also answers "plan_stages", "plan_warps", "plan_chunk_bytes",
+ * "plan_smem_bytes", "plan_hash_bits", "plan_ctas_per_sm" (the plan of the most recent search or
+ * prepare), "last_cluster_size", "last_scheduled", "frontier_size", "grid_cap", "deg_pad".
+ * Returns CORAL_ERR_ARG for unknown names. */
 int coral_set_option(coral_index_t* h, const char* name, int value);
 int coral_get_option(coral_index_t* h, const char* name, int* value);
 
