@@ -45,6 +45,7 @@ struct Options {
     int scout_ids = 0;     // neighbour ids per lane per scout step: 0 = automatic (4; 1 in cluster mode), else 1..4
     int visit_cache_bits = 0;  // shared-memory cache of recently seen ids in front of the visited table (log2 entries)
     int sort_tile = 0;     // candidate sort tile in keys: 0 = automatic (about twice the beam capacity)
+    int probe_carry = 1;   // carry ids the first probe pair leaves open into the next scout step (0 = settle them at once)
     int gather = 0;        // row chunks to shared memory: 0 = one bulk copy per row chunk, 1 = 16-byte unit copies
     int schedule = 0;      // order large batches for L2 locality: 0 = automatic (batches >= 8192), 1 = always, -1 = never
 };
@@ -203,6 +204,7 @@ bool make_plan_warps(const coral_index* h, int L, int warps, SearchPlan& p, std:
     p.hs_bits = std::min(std::max(o.smem_hash_bits, 0), 16);
     p.vc_bits = std::min(std::max(o.visit_cache_bits, 0), 14);
     p.gather = o.gather == 1 ? 1 : 0;
+    p.carry = o.probe_carry != 0 ? 1 : 0;
 
     const int budget = h->smem_optin / p.ctas_per_sm - 1024;  // the runtime keeps 1 KB per CTA
     for (;;) {
@@ -593,6 +595,7 @@ int coral_set_option(coral_index_t* h, const char* name, int value) {
     else if (s == "sort_tile") o.sort_tile = value;
     else if (s == "visit_cache_bits") o.visit_cache_bits = value;
     else if (s == "gather") o.gather = value;
+    else if (s == "probe_carry") o.probe_carry = value;
     else return fail(h, CORAL_ERR_ARG, "unknown option " + s);
     h->plans.clear();
     return CORAL_OK;
@@ -614,6 +617,7 @@ int coral_get_option(coral_index_t* h, const char* name, int* value) {
     else if (s == "last_cluster_size") *value = h->last_cluster_size;
     else if (s == "schedule") *value = o.schedule;
     else if (s == "gather") *value = o.gather;
+    else if (s == "probe_carry") *value = o.probe_carry;
     else if (s == "sort_tile") *value = o.sort_tile;
     else if (s == "scout_ids") *value = o.scout_ids;
     else if (s == "visit_cache_bits") *value = o.visit_cache_bits;

@@ -38,6 +38,8 @@ namespace {
 
 constexpr int kScoutAhead = 64; // a scout step may start while fewer than this many ids are waiting
 constexpr int kIdsPerLane = 4;  // neighbour ids examined per lane per scout step
+constexpr int kMergeAhead = 4; // candidate passes whose keys are fetched together at the end of a round
+constexpr int kProbeSlots = kIdsPerLane + 1;  // ids a lane probes per scout step: the new ones + one carried over
 constexpr int kSmemProbes = 8;
 constexpr int kGlobalProbes = 256;
 constexpr uint32_t kEmpty32 = 0xFFFFFFFFu;
@@ -497,18 +499,23 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
                 // A scout step is split in two: its compare-and-swaps are issued and the warp goes back to
                 // gathering and distances; their answers (which take microseconds under load) are only
                 // looked at when the warp runs short of ids.
+                // An id that its first pair of slots does not settle (both taken by other ids, or the
+                // slot lost to another id) is carried into the lane's next step, which probes the next
+                // pair for it, instead of walking the probe sequence with the warp waiting.
                 bool sc_pending = false;
                 uint32_t sc_cas = 0u;              // bit t: a compare-and-swap is in flight for sv[t]
-                int sv[kIdsPerLane];
-                unsigned long long scur[kIdsPerLane], sold[kIdsPerLane];
+                int sv[kProbeSlots];               // [kIdsPerLane] is the carried id
+                unsigned long long scur[kProbeSlots], sold[kProbeSlots];
+                int carry_att = 0;                 // pair of the probe sequence the carried id tries next
+                bool has_carry = false;            // some lane of the warp carries an id
 #pragma unroll
-                for (int t = 0; t < kIdsPerLane; ++t) {
+                for (int t = 0; t < kProbeSlots; ++t) {
                     sv[t] = -1;
                     scur[t] = sold[t] = 0ull;
                 }
                 for (;;) {
                     // form gather batches from pending ids
-                    while (formed - done < 2u && (pend_n >= 32 || (!more && !sc_pending && pend_n > 0))) {
+                    while (formed - done < 2u && (pend_n >= 32 || (!more && !sc_pending && !has_carry && pend_n > 0))) {
                         const int m = pend_n < 32 ? pend_n : 32;
                         const int slot = formed & 1u;
                         if (lane < m && CORAL_CHECK(pend_n - m + lane >= 0 && pend_n - m + lane < kPendCap, 2, pend_n, m))
@@ -561,55 +568,72 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
                         }
                     }
                     if (sc_pending && pend_n < 32 && formed - done < 2u) {
-                        // ---- scout, second half: read the answers, settle what the first slot left open
-                        bool isnew[kIdsPerLane];
+                        // ---- scout, second half: read the answers; an id its pair did not settle is carried
+                        bool isnew[kProbeSlots];
+                        int carry_id = -1, carry_next = 0;
 #pragma unroll
-                        for (int t = 0; t < kIdsPerLane; ++t) {
+                        for (int tt = 0; tt < kProbeSlots; ++tt) {
+                            const int t = tt == 0 ? kIdsPerLane : tt - 1;   // the carried id first: it may free the carry slot
                             isnew[t] = false;
                             // Keeps the comparison below from being scheduled next to the compare-and-swap
                             // (where it would wait for the answer the first half was written to not wait for).
                             asm volatile("" : "+l"(scur[t]));
                             if (sv[t] >= 0) {
-                                int r = 3;   // 0 new, 1 seen, 2 table full, 3 = the first slot did not settle it
+                                int r = 3;   // 0 new, 1 seen, 2 table full, 3 = this pair did not settle it
+                                bool pair_full = false;
                                 if ((sc_cas >> t) & 1u) {
                                     if (sold[t] == scur[t]) {
                                         r = 0;
                                         ++n_spill;
                                     } else if (sold[t] == (((unsigned long long)epoch << 32) | (uint32_t)sv[t])) {
                                         r = 1;   // the same id won the slot first (another lane or warp)
-                                    }
+                                    }            // else: lost to another id, the pair is looked at again
                                 } else if ((uint32_t)scur[t] == (uint32_t)sv[t]) {
-                                    r = 1;   // the slot held this id with this query's epoch
+                                    r = 1;       // the slot held this id with this query's epoch
+                                } else {
+                                    pair_full = true;
                                 }
-                                if (r == 3) r = visited_insert(shash, 0, ghash, a.gh_mask, epoch, sv[t], n_spill);
+                                if (r == 3) {
+                                    const int att = (t == kIdsPerLane ? carry_att : 0) + (pair_full ? 1 : 0);
+                                    if (P.carry && carry_id < 0 && att < kGlobalProbes / 2) {
+                                        carry_id = sv[t];
+                                        carry_next = att;
+                                    } else {
+                                        r = visited_insert(shash, 0, ghash, a.gh_mask, epoch, sv[t], n_spill);
+                                    }
+                                }
                                 isnew[t] = r == 0;
                                 if (r == 2) overflow = true;
                             }
                         }
 #pragma unroll
-                        for (int t = 0; t < kIdsPerLane; ++t) {
+                        for (int t = 0; t < kProbeSlots; ++t) {
                             const uint32_t m = __ballot_sync(0xffffffffu, isnew[t]);
                             if (isnew[t] && CORAL_CHECK(pend_n + __popc(m & lt_mask) < kPendCap, 5, pend_n, m))
                                 pend[pend_n + __popc(m & lt_mask)] = sv[t];
                             pend_n += __popc(m);
                         }
+                        sv[kIdsPerLane] = carry_id;
+                        carry_att = carry_next;
+                        has_carry = __any_sync(0xffffffffu, carry_id >= 0);
                         sc_pending = false;
                         __syncwarp();
                         continue;
                     }
-                    if (more && !sc_pending && pend_n < kScoutAhead) {
+                    if ((more || has_carry) && !sc_pending && pend_n < kScoutAhead) {
                         // ---- scout, first half: adjacency rows of the next slots, visited-table probes
                         int s0 = 0;
-                        if (lane == 0) s0 = atomicAdd(p_exp_next, step_slots);
-                        s0 = __shfl_sync(0xffffffffu, s0, 0);
                         const int total_slots = exp_count << a.deg_shift;
-                        if (s0 >= total_slots) {
-                            more = false;
-                            continue;
-                        }
-                        if (lane == 0) {   // entries whose first slot falls into this step
-                            const int s1 = s0 + step_slots < total_slots ? s0 + step_slots : total_slots;
-                            n_exp += ((s1 + a.deg_pad - 1) >> a.deg_shift) - ((s0 + a.deg_pad - 1) >> a.deg_shift);
+                        if (more) {
+                            if (lane == 0) s0 = atomicAdd(p_exp_next, step_slots);
+                            s0 = __shfl_sync(0xffffffffu, s0, 0);
+                            if (s0 >= total_slots) {
+                                more = false;
+                                if (!has_carry) continue;
+                            } else if (lane == 0) {   // entries whose first slot falls into this step
+                                const int s1 = s0 + step_slots < total_slots ? s0 + step_slots : total_slots;
+                                n_exp += ((s1 + a.deg_pad - 1) >> a.deg_shift) - ((s0 + a.deg_pad - 1) >> a.deg_shift);
+                            }
                         }
                         int v[kIdsPerLane];
 #pragma unroll
@@ -617,7 +641,7 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
                             const int slot = s0 + lane + 32 * t;
                             const int ent = slot >> a.deg_shift;
                             v[t] = -1;
-                            if (t < ipl && ent < exp_count) {
+                            if (more && t < ipl && ent < exp_count) {
                                 const int node = CLUSTER ? __ldcg(gexp + ent) : exp_list[ent];
                                 if (CORAL_CHECK(ent < a.L && node >= 0 && (int64_t)node < a.n, 4, node, ent))
                                     v[t] = __ldg(a.adj + (size_t)node * a.deg_pad + (slot & (a.deg_pad - 1)));
@@ -630,17 +654,24 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
                             // The probe sequence of an id starts on an aligned pair of slots, read with
                             // one 16-byte load: only when both hold other ids of this query (rare at the
                             // table's load) is the id left to the full probe in the second half.
-                            unsigned long long* slot[kIdsPerLane];
-                            ulonglong2 pair[kIdsPerLane];
+                            unsigned long long* slot[kProbeSlots];
+                            ulonglong2 pair[kProbeSlots];
 #pragma unroll
-                            for (int t = 0; t < kIdsPerLane; ++t) {
-                                sv[t] = -1;
+                            for (int t = 0; t < kProbeSlots; ++t) {
                                 slot[t] = nullptr;
                                 pair[t] = make_ulonglong2(0ull, 0ull);
-                                if (v[t] >= 0 && (int64_t)v[t] < a.n) {
-                                    ++n_scan;
-                                    sv[t] = v[t];
-                                    slot[t] = (unsigned long long*)&ghash[mix32((uint32_t)v[t]) & a.gh_mask & ~1u];
+                                int att = 0;
+                                if (t < kIdsPerLane) {
+                                    sv[t] = -1;
+                                    if (v[t] >= 0 && (int64_t)v[t] < a.n) {
+                                        ++n_scan;
+                                        sv[t] = v[t];
+                                    }
+                                } else {
+                                    att = carry_att;   // sv[t] still holds the carried id (or -1)
+                                }
+                                if (sv[t] >= 0) {
+                                    slot[t] = (unsigned long long*)&ghash[((mix32((uint32_t)sv[t]) & ~1u) + 2u * (uint32_t)att) & a.gh_mask];
                                     asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];"
                                                  : "=l"(pair[t].x), "=l"(pair[t].y)
                                                  : "l"(slot[t])
@@ -649,7 +680,7 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
                             }
                             sc_cas = 0u;
 #pragma unroll
-                            for (int t = 0; t < kIdsPerLane; ++t) {
+                            for (int t = 0; t < kProbeSlots; ++t) {
                                 scur[t] = ~0ull;   // "not settled by the pair": the full probe decides later
                                 if (sv[t] >= 0) {
                                     const bool mine0 = (uint32_t)(pair[t].x >> 32) == epoch;
@@ -743,7 +774,7 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
                         }
                         continue;
                     }
-                    if (!more && !sc_pending && pend_n == 0) break;
+                    if (!more && !has_carry && !sc_pending && pend_n == 0) break;
                 }
             }
             if (CLUSTER) {
@@ -771,30 +802,59 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
                 __syncthreads();
                 int fill = 0;
                 while (pos < C && fill + nthreads <= P.tile_max) {
-                    const int i = pos + tid;
-                    int taken = 0;
-                    if (i < C) {
-                        const uint64_t key = __ldcg(gcand + i);
-                        if (key < bound) {
-                            const int slot = atomicAdd(&S.fill, 1);
-                            if (CORAL_CHECK(slot < P.tile_max && key_id(key) >= 0 && (int64_t)key_id(key) < a.n, 6, slot, key))
-                                sortbuf[slot] = key;
-                            taken = 1;
+                    // The keys of the next kMergeAhead passes are fetched together (one trip to L2
+                    // for all of them); a pass that no longer fits the tile is fetched again later.
+                    uint64_t ahead[kMergeAhead];
+#pragma unroll
+                    for (int j = 0; j < kMergeAhead; ++j) {
+                        const int i = pos + j * nthreads + tid;
+                        ahead[j] = i < C ? __ldcg(gcand + i) : kPadKey;
+                    }
+#pragma unroll
+                    for (int j = 0; j < kMergeAhead; ++j) {
+                        if (pos < C && fill + nthreads <= P.tile_max) {
+                            int taken = 0;
+                            const uint64_t key = ahead[j];
+                            if (pos + tid < C && key < bound) {
+                                const int slot = atomicAdd(&S.fill, 1);
+                                if (CORAL_CHECK(slot < P.tile_max && key_id(key) >= 0 && (int64_t)key_id(key) < a.n, 6, slot, key))
+                                    sortbuf[slot] = key;
+                                taken = 1;
+                            }
+                            pos += nthreads;
+                            // The tile's fill level must be the same number in every thread: it decides
+                            // whether another pass runs.  Reading S.fill back after the barrier would
+                            // race with the next pass's atomicAdd of faster threads; the barrier's own
+                            // count cannot.
+                            fill += __syncthreads_count(taken);
                         }
                     }
-                    pos += nthreads;
-                    // The tile's fill level must be the same number in every thread: it decides
-                    // whether another pass runs.  Reading S.fill back after the barrier would race
-                    // with the next pass's atomicAdd of faster threads; the barrier's own count
-                    // cannot.
-                    fill += __syncthreads_count(taken);
                 }
                 if (fill == 0) continue;
                 int n2 = 32;
                 while (n2 < fill) n2 <<= 1;
                 for (int i = fill + tid; i < n2; i += nthreads) sortbuf[i] = kPadKey;
                 __syncthreads();
-                bitonic_sort(sortbuf, n2, tid, nthreads);
+                if (n2 == 32) {
+                    // a tile of at most 32 keys (the usual case once the L-th key has tightened the
+                    // filter): one warp sorts it in registers, no barrier per stage
+                    if (warp == 0) {
+                        uint64_t x = sortbuf[lane];
+#pragma unroll
+                        for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+                            for (int j = k >> 1; j > 0; j >>= 1) {
+                                const uint64_t y = __shfl_xor_sync(0xffffffffu, x, j);
+                                const bool keep_min = ((lane & j) == 0) == ((lane & k) == 0);
+                                x = keep_min ? (x < y ? x : y) : (x < y ? y : x);
+                            }
+                        }
+                        sortbuf[lane] = x;
+                    }
+                    __syncthreads();
+                } else {
+                    bitonic_sort(sortbuf, n2, tid, nthreads);
+                }
                 // merge by rank: beam[0..cnt) and sortbuf[0..fill), both ascending, keys distinct
                 for (int i = tid; i < cnt; i += nthreads) {
                     const uint64_t x = beam[i];

@@ -24,6 +24,7 @@ struct SearchPlan {
     int tile_max;     // largest candidate tile sorted at once (power of two)
     int ctas_per_sm;
     int gather;       // how row chunks reach shared memory: 0 = one bulk copy per row chunk, 1 = 16-byte unit copies
+    int carry;        // 1 = an id its first probe pair does not settle is carried into the lane's next scout step
     int off_query, off_beam0, off_beam1, off_exp, off_hash, off_vcache, off_bar, off_pend, off_bids, off_stage;
     int smem_bytes;
 };

@@ -73,6 +73,7 @@ bool plan_for(int dim, int L, int smem_optin, coral::SearchPlan& p) {
     p.stage_bytes = 32 * p.row_stride;
     p.stages = 1;
     p.hs_bits = 0;
+    p.carry = 1;
     p.LP = next_pow2(L > 32 ? L : 32);
     int off = 0;
     p.off_query = off;  off = align_up(off + dim * 4, 16);

@@ -8,7 +8,10 @@
 // --max_hop --k --max_degree --query_thres --log_file --res_file --config_file
 // --CE --index_type, plus -T (accepted, unused, like the reference).
 // Additions: --graph_path DIR (instead of ../indexes/<dataset>_<dist>_<deg>_<thres>_<CE>),
-// --roar_graph FILE (flat graph import), --csv FILE, --device N, --ids_out FILE.
+// --roar_graph FILE (flat graph import), --csv FILE, --device N, --ids_out FILE,
+// --deleted_ids FILE (text list of ids hidden from the results, IndexGPU::SetDeleted),
+// --verify (count hits on the device with IndexGPU::Search_and_Verify, needs a
+// ground truth exactly k wide; prints "hits <n>" per sweep point).
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
@@ -102,6 +105,13 @@ int main(int argc, char** argv) {
         std::cout << "Load graph index: " << graph_dir << std::endl;
         index.RunPrepare(parameters, Mode::SEARCH);
         if (has("roar_graph")) index.LoadRoarGraph(str("roar_graph", ""));
+        if (has("deleted_ids")) {
+            std::ifstream in(str("deleted_ids", ""));
+            if (!in.is_open()) throw std::runtime_error("cannot open " + str("deleted_ids", ""));
+            std::vector<int> dead;
+            for (long long v; in >> v;) dead.push_back((int)v);
+            index.SetDeleted(dead);
+        }
 
         std::cout << "k: " << k << std::endl;
         std::vector<int> res(qm.n * (size_t)k, 0);
@@ -125,6 +135,11 @@ int main(int argc, char** argv) {
             const float avg_hops = tr.avg_hops((int)qm.n);
             std::cout << L << "\t\t" << qps << "\t\t" << time << "\t\t" << recall << "\t\t" << avg_hops << std::endl;
             if (csv.is_open()) csv << L << "," << qps << "," << time << "," << recall << "," << avg_hops << std::endl;
+            if (opt.count("verify")) {   // src/index_gpu.cpp:89-115: search + hit count on the device
+                if (gt.k != k) throw std::runtime_error("--verify needs a ground truth exactly k wide");
+                const Test_Result tv = index.Search_and_Verify(query_data, gt.ids.data(), nq, L);
+                std::cout << "hits " << tv.hits << std::endl;
+            }
             if (max_recall > 0.5 && recall < max_recall) L_vec.push_back(128 + L_vec.back());  // :308-310
             if (i > 50) break;
         }

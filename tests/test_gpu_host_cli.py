@@ -102,3 +102,55 @@ def test_driver_selects_and_saves_entry_points_when_none_are_stored(tmp_path):
     ids = np.fromfile(tmp_path / "ids.bin", dtype=np.int32).reshape(len(c.queries), k)
     ref_ids, _, _ = oracle.search(c.base, c.adj, want, c.queries, 64, k, "l2")
     assert np.array_equal(ids, ref_ids)
+
+
+def test_driver_flat_graph_import_deleted_ids_and_device_hit_count(tmp_path):
+    """IndexGPU::LoadRoarGraph (flat graph, single entry point), SetDeleted and Search_and_Verify
+    through the driver: ids equal the oracle's with the deleted ids skipped, and the hit count
+    made on the device equals the recall sum computed from those ids."""
+    import ctypes as C
+    build_host.build()
+    c = cases.structured("l2")
+    k, L = 10, 64
+    lib = C.CDLL(build_host.HOST_LIB)
+    lib.coral_host_flat_graph_roundtrip.argtypes = [C.c_char_p, C.c_int64, C.c_int, C.c_int, C.c_void_p, C.c_int32,
+                                                    C.c_void_p, C.POINTER(C.c_int32)]
+    lib.coral_host_flat_graph_roundtrip.restype = C.c_int
+    ep = int(c.start[3])
+    back = np.empty_like(c.adj)
+    ep_back = C.c_int32(-1)
+    dp = lib.coral_host_flat_graph_roundtrip(str(tmp_path / "flat.bin").encode(), c.n, c.adj.shape[1], 32,
+                                             c.adj.ctypes.data, ep, back.ctypes.data, C.byref(ep_back))
+    assert dp == c.adj.shape[1] and ep_back.value == ep
+    (tmp_path / "base.fbin").write_bytes(struct.pack("<ii", c.n, c.dim) + c.base.tobytes())
+    (tmp_path / "query.fbin").write_bytes(struct.pack("<ii", len(c.queries), c.dim) + c.queries.tobytes())
+    # any graph directory satisfies RunPrepare; the flat graph replaces it afterwards
+    degs = (c.adj >= 0).sum(1)
+    write_reference_graph_dir(str(tmp_path / "graph"), degs, c.adj, _literal_block)
+    (tmp_path / "graph" / "graph.search_start_ids").write_text("1 0 ")
+    (tmp_path / "config.json").write_text('{"dim": %d, "k": %d}' % (c.dim, k))
+    start = np.array([ep], np.int32)
+    full_ids, _, _ = oracle.search(c.base, c.adj, start, c.queries, L, L, "l2")
+    dead = sorted({int(v) for v in full_ids[:, 0] if v >= 0})      # hide every query's best hit
+    (tmp_path / "dead.txt").write_text(" ".join(map(str, dead)))
+    want = np.full((len(c.queries), k), -1, np.int32)
+    for qi in range(len(c.queries)):
+        keep = [v for v in full_ids[qi] if v >= 0 and v not in set(dead)][:k]
+        want[qi, :len(keep)] = keep
+    gt = want.copy()                                                # ground truth exactly k wide
+    gt[:, ::2] = 0                                                  # half of it wrong on purpose
+    (tmp_path / "gt.bin").write_bytes(struct.pack("<ii", gt.shape[0], gt.shape[1]) + gt.astype(np.int32).tobytes())
+    exe = os.path.join(os.path.dirname(build_host.HOST_LIB), "test_search_pipeline")
+    cmd = [exe, "--dataset", "synthetic", "--data_type", "float", "--dist", "l2",
+           "--base_data_path", str(tmp_path / "base.fbin"), "--query_path", str(tmp_path / "query.fbin"),
+           "--gt_path", str(tmp_path / "gt.bin"), "--graph_path", str(tmp_path / "graph"),
+           "--roar_graph", str(tmp_path / "flat.bin"), "--deleted_ids", str(tmp_path / "dead.txt"), "--verify",
+           "--config_file", str(tmp_path / "config.json"), "--max_degree", "32", "--k", str(k),
+           "--L", str(L), "--ids_out", str(tmp_path / "ids.bin")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    ids = np.fromfile(tmp_path / "ids.bin", dtype=np.int32).reshape(len(c.queries), k)
+    assert np.array_equal(ids, want)
+    hits = [int(ln.split()[1]) for ln in r.stdout.splitlines() if ln.startswith("hits ")]
+    expect = sum(sum(1 for p in gt[qi] if p in ids[qi]) for qi in range(len(c.queries)))
+    assert hits == [expect]

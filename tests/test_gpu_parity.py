@@ -105,6 +105,8 @@ def test_underfull_beam_is_reported_not_faulted():
     {"gather": 1, "stages": 3, "chunk_bytes": 128, "warps": 3},
     {"gather": 1, "chunk_bytes": 1024, "warps": 2, "ctas_per_sm": 1},   # more units per chunk than lanes
     {"gather": 0, "stages": 2},
+    {"probe_carry": 0},                            # ids the first probe pair leaves open are settled at once
+    {"probe_carry": 1, "ghash_entries": 4096},     # a crowded visited table: many carried probes
 ])
 def test_tuning_knobs_do_not_change_results(opts):
     c = cases.structured("ip")
