@@ -51,8 +51,8 @@ PEAK_FALLBACK_GBS = 6650.0
 # DRAM bytes moved by one full-size launch, from the single-pass ncu capture recorded in
 # profiles/ (workload, L) -> bytes; absent -> null in the JSON line.
 MEASURED_TRAFFIC = {
-    ("c3", 64): 3.771e11,      # dram__bytes_read 351.4 GB + dram__bytes_write 25.7 GB for 100k queries (locality-scheduled)
-    ("small", 64): 1.131e10,   # 9.94 GB + 1.37 GB for 8192 queries
+    ("c3", 64): 3.916e11,      # dram__bytes_read 366.0 GB + dram__bytes_write 25.6 GB for 100k queries (locality-ordered)
+    ("small", 64): 1.201e10,   # 10.64 GB + 1.37 GB for 8192 queries
 }
 
 
