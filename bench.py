@@ -200,37 +200,58 @@ def run_latency(args, w, ix, ds, g, device, rank):
     recall = ix.count_hits(ids, gt, k) / float(k * n_gt)
     stream = torch.cuda.Stream(device=device)
     h_all = ds.test.cpu().pin_memory()
-    table = {}
     launches0 = ix.launch_count
-    for B in w["latency"]:
-        d_ids = torch.empty((B, k), dtype=torch.int32, device=device)
-        h_ids = torch.empty((B, k), dtype=torch.int32).pin_memory()
-        n_batches = max(20, min(200, w["q"] // B))
-        dev_us, e2e_us = [], []
-        hops = C.c_int64(0)
-        for i in range(n_batches + args.warmup):
-            s = (i * B) % (w["q"] - B + 1)
-            q = ds.test[s:s + B]
-            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            ev0.record(stream)
-            ix.search_async(q, L, k, d_ids, None, None, stream.cuda_stream)
-            ev1.record(stream)
-            stream.synchronize()
-            hq = h_all[s:s + B].numpy()
-            t0 = time.perf_counter()
-            rc = lib.coral_search(handle, C.c_void_p(hq.ctypes.data), B, L, k, C.c_void_p(h_ids.numpy().ctypes.data),
-                                  None, None, C.byref(hops))
-            t1 = time.perf_counter()
-            if rc != 0:
-                raise RuntimeError(lib.coral_last_error(handle).decode())
-            if i >= args.warmup:
-                dev_us.append(ev0.elapsed_time(ev1) * 1e3)
-                e2e_us.append((t1 - t0) * 1e6)
-        ix.check()
-        table[B] = {"p50_us": float(np.percentile(dev_us, 50)), "p99_us": float(np.percentile(dev_us, 99)),
-                    "e2e_p50_us": float(np.percentile(e2e_us, 50)), "e2e_p99_us": float(np.percentile(e2e_us, 99)),
-                    "qps": B / float(np.percentile(dev_us, 50)) * 1e6, "batches": n_batches,
-                    "ctas_per_query": ix.get_option("last_cluster_size")}
+
+    def measure():
+        table = {}
+        for B in w["latency"]:
+            d_ids = torch.empty((B, k), dtype=torch.int32, device=device)
+            h_ids = torch.empty((B, k), dtype=torch.int32).pin_memory()
+            n_batches = max(20, min(200, w["q"] // B))
+            dev_us, e2e_us = [], []
+            hops = C.c_int64(0)
+            for i in range(n_batches + args.warmup):
+                s = (i * B) % (w["q"] - B + 1)
+                q = ds.test[s:s + B]
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record(stream)
+                ix.search_async(q, L, k, d_ids, None, None, stream.cuda_stream)
+                ev1.record(stream)
+                stream.synchronize()
+                hq = h_all[s:s + B].numpy()
+                t0 = time.perf_counter()
+                rc = lib.coral_search(handle, C.c_void_p(hq.ctypes.data), B, L, k, C.c_void_p(h_ids.numpy().ctypes.data),
+                                      None, None, C.byref(hops))
+                t1 = time.perf_counter()
+                if rc != 0:
+                    raise RuntimeError(lib.coral_last_error(handle).decode())
+                if i >= args.warmup:
+                    dev_us.append(ev0.elapsed_time(ev1) * 1e3)
+                    e2e_us.append((t1 - t0) * 1e6)
+            ix.check()
+            table[B] = {"p50_us": float(np.percentile(dev_us, 50)), "p99_us": float(np.percentile(dev_us, 99)),
+                        "e2e_p50_us": float(np.percentile(e2e_us, 50)), "e2e_p99_us": float(np.percentile(e2e_us, 99)),
+                        "qps": B / float(np.percentile(dev_us, 50)) * 1e6, "batches": n_batches,
+                        "ctas_per_query": ix.get_option("last_cluster_size")}
+        return table
+
+    table = measure()
+    # The same batches with 10 % of the points deleted (tombstones only: the reference's deleted-bitset
+    # overload hides them from the results, src/search_gpu.cu:716; its topology repair and the insert
+    # path are not part of this build, so this is not the reference's "after delete + insert" state).
+    rng = np.random.default_rng(77)
+    dead = rng.random(w["n"]) < 0.10
+    bits = np.packbits(dead, bitorder="little")
+    bits = np.concatenate([bits, np.zeros((-len(bits)) % 4, np.uint8)]).view(np.uint32)
+    gt_wide = synth.exact_knn(ds.base, ds.test[:n_gt], 4 * k, w["metric"]).cpu().numpy()
+    gt_alive = np.stack([row[~dead[row]][:k] for row in gt_wide])
+    ix.set_deleted(bits)
+    ids_d, _, _, _ = ix.search(ds.test[:n_gt], L, k, dists=False)
+    ids_d = ids_d.cpu().numpy() if hasattr(ids_d, "cpu") else np.asarray(ids_d)
+    assert not dead[ids_d[ids_d >= 0]].any(), "a deleted id was returned"
+    recall_deleted = float(np.mean([len(set(a) & set(b)) / k for a, b in zip(ids_d, gt_alive)]))
+    table_deleted = measure()
+    ix.set_deleted(None)
     if rank == 0:
         b1 = table[w["latency"][0]]
         out = {"metric": "p50 latency of one query batch, 10Mx512 IP, L=%d" % L, "value": b1["p50_us"], "unit": "us",
@@ -238,6 +259,7 @@ def run_latency(args, w, ix, ds, g, device, rank):
                "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                "config": {"workload": args.workload, "n": w["n"], "dim": dim, "metric": w["metric"], "max_degree": w["deg"],
                           "k": k, "L": L, "recall": recall, "batch_sizes": w["latency"], "latency": table,
+                          "latency_with_10pct_deleted": table_deleted, "recall_with_10pct_deleted": recall_deleted,
                           "l2_policy": "inputs larger than L2; every batch uses different queries"},
                "e2e": {"value": b1["e2e_p50_us"], "unit": "us", "h2d_bytes_per_step": dim * 4 * w["latency"][0],
                        "d2h_bytes_per_step": k * 4 * w["latency"][0] + 32},
