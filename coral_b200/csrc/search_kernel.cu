@@ -549,16 +549,16 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
                             }
                             ldgsts_commit();
                         } else {
-                        if (lane == 0) mbar_expect_tx(&bars[st], (uint32_t)cnt * (uint32_t)P.chunk_bytes);
-                        __syncwarp();
-                        if (lane < cnt) {
-                            int id = bids[(b & 1u) * 32 + lane];
-                            if (!CORAL_CHECK(id >= 0 && (int64_t)id < a.n && cnt <= 32 && (int)st < P.stages, 3, id, cnt)) id = 0;
-                            bulk_g2s(stage0 + (size_t)st * P.stage_bytes + (size_t)lane * P.row_stride,
-                                     reinterpret_cast<const unsigned char*>(a.vecs) + (size_t)id * row_bytes +
-                                         (size_t)c * P.chunk_bytes,
-                                     (uint32_t)P.chunk_bytes, &bars[st]);
-                        }
+                            if (lane == 0) mbar_expect_tx(&bars[st], (uint32_t)cnt * (uint32_t)P.chunk_bytes);
+                            __syncwarp();
+                            if (lane < cnt) {
+                                int id = bids[(b & 1u) * 32 + lane];
+                                if (!CORAL_CHECK(id >= 0 && (int64_t)id < a.n && cnt <= 32 && (int)st < P.stages, 3, id, cnt)) id = 0;
+                                bulk_g2s(stage0 + (size_t)st * P.stage_bytes + (size_t)lane * P.row_stride,
+                                         reinterpret_cast<const unsigned char*>(a.vecs) + (size_t)id * row_bytes +
+                                             (size_t)c * P.chunk_bytes,
+                                         (uint32_t)P.chunk_bytes, &bars[st]);
+                            }
                         }
                         ++inflight;
                         iss_st = iss_st + 1 == P.stages ? 0 : iss_st + 1;
