@@ -16,17 +16,17 @@ from . import build as _build
 L2, IP = 0, 1
 STATS_W = 8
 STAT_NAMES = ("status", "n_dist", "n_exp", "rounds", "hops", "n_scan", "max_cand", "n_spill")
-OK, ERR_ARG, ERR_STATE, ERR_CUDA, ERR_NOGPU, ERR_KERNEL, ERR_LIMIT = range(7)
+OK, ERR_ARG, ERR_STATE, ERR_CUDA, ERR_NOGPU, ERR_KERNEL, ERR_LIMIT, ERR_QUERY = range(8)
 
 EXPORTS = (
-    "coral_version", "coral_compiled_sm", "coral_index_create", "coral_index_destroy",
+    "coral_version", "coral_compiled_sm", "coral_plan", "coral_index_create", "coral_index_destroy",
     "coral_index_set_vectors", "coral_index_attach_vectors", "coral_index_set_slots",
     "coral_index_set_adjacency", "coral_index_set_start_ids", "coral_index_select_start_ids",
     "coral_index_set_deleted",
     "coral_search_prepare", "coral_search_free", "coral_search", "coral_search_async",
     "coral_search_check", "coral_last_kernel_ms", "coral_last_total_ms", "coral_launch_count",
     "coral_set_option", "coral_get_option", "coral_count_hits", "coral_merge_shards",
-    "coral_map_ids", "coral_last_error", "coral_search_static",
+    "coral_map_ids", "coral_last_error", "coral_search_static", "coral_search_static_status",
 )
 
 _lib = None
@@ -53,6 +53,7 @@ def load():
     sig = {
         "coral_version": (C.c_int, []),
         "coral_compiled_sm": (C.c_int, []),
+        "coral_plan": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int)]),
         "coral_index_create": (C.c_int, [C.POINTER(vp), C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int]),
         "coral_index_destroy": (C.c_int, [vp]),
         "coral_index_set_vectors": (C.c_int, [vp, f32p]),
@@ -78,6 +79,7 @@ def load():
         "coral_last_error": (C.c_char_p, [vp]),
         "coral_search_static": (C.c_int, [C.c_int, vp, f32p, i32p, C.c_int64, C.c_int, C.c_int, C.c_int, i32p, C.c_int,
                                           f32p, C.c_int, C.c_int, C.c_int, i32p, f32p]),
+        "coral_search_static_status": (C.c_int, [C.c_int]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "../../include/coral_b200.h"
+#include "plan.cuh"
 #include "schedule.cuh"
 #include "search_kernel.cuh"
 #include "start_select.cuh"
@@ -140,120 +141,18 @@ int next_pow2(int x) {
     return p;
 }
 
-int align_up(int x, int a) { return (x + a - 1) / a * a; }
-
-// Shared-memory plan for beam capacity L; returns false when nothing fits.
-bool make_plan_warps(const coral_index* h, int L, int warps, SearchPlan& p, std::string& why, int chunk_target = 0);
-
-// With warps = 0 the warp count per CTA is chosen to maximise resident warps per SM
-// (CTAs per SM x warps), preferring more CTAs on a tie: on 10M x 512 the achieved bandwidth
-// followed that product (16 warps/SM 0.83, 18 0.87, 20 0.90-0.94 of the measured peak).
-bool make_plan(const coral_index* h, int L, SearchPlan& p, std::string& why) {
-    if (h->opt.warps > 0 || h->opt.ctas_per_sm > 0)
-        return make_plan_warps(h, L, h->opt.warps > 0 ? h->opt.warps : 4, p, why);
-    bool found = false;
-    for (int w : {3, 4, 5, 6}) {
-        SearchPlan q;
-        std::string dummy;
-        if (!make_plan_warps(h, L, w, q, dummy)) continue;
-        const int total = q.ctas_per_sm * q.warps, best = p.ctas_per_sm * p.warps;
-        if (!found || total > best || (total == best && q.ctas_per_sm > p.ctas_per_sm)) p = q;
-        found = true;
-    }
-    if (!found) return make_plan_warps(h, L, 4, p, why);
-    // Every bulk copy costs its warp about 54 cycles to issue whatever its size, so rows that do
-    // not split into 256-byte chunks (dim 200: five chunks of 160 bytes) are better moved in chunks
-    // of up to 512 bytes -- as long as five CTAs still fit an SM (measured on 1M x 200, L = 64:
-    // 1.85M against 1.56M queries/s with 400-byte chunks; at L = 512, where only four CTAs fit,
-    // 160-byte chunks stay ahead).
-    if (h->opt.chunk_bytes <= 0 && p.chunk_bytes < 256) {
-        SearchPlan best{};
-        bool have = false;
-        for (int w : {3, 4, 5, 6}) {
-            SearchPlan q;
-            std::string dummy;
-            if (!make_plan_warps(h, L, w, q, dummy, 512) || q.chunk_bytes <= p.chunk_bytes) continue;
-            const int total = q.ctas_per_sm * q.warps, cur = best.ctas_per_sm * best.warps;
-            if (!have || total > cur || (total == cur && q.ctas_per_sm > best.ctas_per_sm)) best = q;
-            have = true;
-        }
-        if (have && best.ctas_per_sm >= 5) p = best;
-    }
-    return true;
-}
-
-bool make_plan_warps(const coral_index* h, int L, int warps, SearchPlan& p, std::string& why, int chunk_target) {
-    const Options& o = h->opt;
-    const int row_bytes = h->dim * 4;
-    p = SearchPlan{};
-    p.warps = std::min(std::max(warps, 1), 16);
-    const bool auto_ctas = o.ctas_per_sm <= 0;
-    p.ctas_per_sm = auto_ctas ? 1 : std::min(o.ctas_per_sm, 8);
-    int target = std::max(16, chunk_target > 0 ? chunk_target : (o.chunk_bytes > 0 ? o.chunk_bytes : 256));
-    int nc = (row_bytes + target - 1) / target;
-    while (nc <= row_bytes / 16 && !(row_bytes % nc == 0 && (row_bytes / nc) % 16 == 0)) ++nc;
-    if (nc > row_bytes / 16) {
-        why = "row size has no 16-byte chunking";
-        return false;
-    }
-    p.n_chunks = nc;
-    p.chunk_bytes = row_bytes / nc;
-    p.row_stride = p.chunk_bytes + (((p.chunk_bytes / 16) % 2 == 0) ? 16 : 0);
-    p.stage_bytes = 32 * p.row_stride;
-    p.LP = next_pow2(std::max(L, 32));
-    p.hs_bits = std::min(std::max(o.smem_hash_bits, 0), 16);
-    p.vc_bits = std::min(std::max(o.visit_cache_bits, 0), 14);
-    p.gather = o.gather == 1 ? 1 : 0;
-    p.carry = o.probe_carry != 0 ? 1 : 0;
-
-    const int budget = h->smem_optin / p.ctas_per_sm - 1024;  // the runtime keeps 1 KB per CTA
-    for (;;) {
-        int off = 0;
-        p.off_query = off;  off = align_up(off + h->dim * 4, 16);
-        p.off_beam0 = off;  off += p.LP * 8;
-        p.off_beam1 = off;  off += p.LP * 8;
-        p.off_exp = off;    off = align_up(off + L * 4, 16);
-        p.off_hash = off;   off += p.hs_bits > 0 ? (4 << p.hs_bits) : 0;
-        p.off_vcache = off; off += p.vc_bits > 0 ? (4 << p.vc_bits) : 0;
-        p.off_bar = off;    off += p.warps * 8 * 8;  // room for up to 8 stages
-        p.off_pend = off;   off += p.warps * coral::kPendCap * 4;
-        p.off_bids = off;   off += p.warps * 64 * 4;
-        off = align_up(off, 128);
-        p.off_stage = off;
-        const int room = budget - off;
-        int st = room / (p.warps * p.stage_bytes);
-        if (o.stages > 0) st = std::min(st, o.stages);
-        else if (auto_ctas) st = std::min(st, 1);
-        st = std::min(st, 6);
-        if (st >= 1) {
-            p.stages = st;
-            p.smem_bytes = off + p.warps * st * p.stage_bytes;
-            break;
-        }
-        if (p.hs_bits > 0) {  // shrink the shared hash before giving up
-            p.hs_bits = p.hs_bits > 8 ? p.hs_bits - 1 : 0;
-            continue;
-        }
-        why = "shared memory budget too small for this dim/L/warps/ctas_per_sm";
-        return false;
-    }
-    if (auto_ctas) p.ctas_per_sm = std::min(std::max(h->smem_optin / (p.smem_bytes + 1024), 1), 8);
-    // Candidate sort tile.  Only the L best of a round's candidates survive, and after each tile is
-    // merged the L-th key tightens the filter for the rest, so small tiles (about 2L) sort far
-    // fewer keys in total than one big tile: a round with 1500 candidates and L = 64 sorts ~300
-    // keys in 256-key tiles instead of 2048.  Bounded by the staging memory the tile lives in.
-    int tile = 64;
-    int cap = std::min(p.warps * p.stages * p.stage_bytes / 8, 2048);
-    const int want = o.sort_tile > 0 ? o.sort_tile : std::max(2 * p.LP, next_pow2(p.warps * 32));
-    cap = std::min(cap, std::max(want, p.warps * 32));
-    while (tile * 2 <= cap) tile <<= 1;
-    if (tile < p.warps * 32 && tile * 2 <= std::min(p.warps * p.stages * p.stage_bytes / 8, 2048)) tile <<= 1;
-    p.tile_max = tile;
-    if (p.tile_max < p.warps * 32) {
-        why = "staging area too small to sort a candidate tile";
-        return false;
-    }
-    return true;
+coral::PlanOptions plan_options(const Options& o) {
+    coral::PlanOptions p;
+    p.ctas_per_sm = o.ctas_per_sm;
+    p.warps = o.warps;
+    p.chunk_bytes = o.chunk_bytes;
+    p.stages = o.stages;
+    p.smem_hash_bits = o.smem_hash_bits;
+    p.visit_cache_bits = o.visit_cache_bits;
+    p.sort_tile = o.sort_tile;
+    p.probe_carry = o.probe_carry;
+    p.gather = o.gather;
+    return p;
 }
 
 // `small_batch`: the batch cannot fill the GPU, so latency per query matters more than
@@ -269,8 +168,10 @@ int get_plan(coral_index* h, int L, SearchPlan& p, int& per_sm, bool small_batch
         per_sm = it->second.second;
         return CORAL_OK;
     }
-    std::string why;
-    const bool ok = (key & 1) ? make_plan_warps(h, L, 8, p, why) : make_plan(h, L, p, why);
+    const char* why = "no plan";
+    const coral::PlanOptions po = plan_options(h->opt);
+    const bool ok = (key & 1) ? coral::make_plan_warps(h->dim, h->smem_optin, po, L, 8, p, &why)
+                              : coral::make_plan(h->dim, h->smem_optin, po, L, p, &why);
     if (!ok) return fail(h, CORAL_ERR_ARG, why);
     per_sm = coral::beam_search_occupancy(p, h->metric);
     if (per_sm <= 0) return fail(h, CORAL_ERR_CUDA, "kernel does not fit an SM with this plan");
@@ -392,7 +293,31 @@ void free_search(coral_index* h) {
 
 extern "C" {
 
-int coral_version(void) { return 100; }
+int coral_version(void) { return 200; }
+
+int coral_plan(int dim, int L, int smem_optin_bytes, int* out8) {
+    if (dim <= 0 || dim % 4 != 0 || L <= 0 || L > 4096 || smem_optin_bytes <= 0 || !out8) return CORAL_ERR_ARG;
+    SearchPlan p;
+    const char* why = nullptr;
+    if (!coral::make_plan(dim, smem_optin_bytes, coral::PlanOptions{}, L, p, &why)) return CORAL_ERR_LIMIT;
+    out8[0] = p.warps;
+    out8[1] = p.ctas_per_sm;
+    out8[2] = p.chunk_bytes;
+    out8[3] = p.n_chunks;
+    out8[4] = p.stages;
+    out8[5] = p.smem_bytes;
+    out8[6] = p.tile_max;
+    out8[7] = p.LP;
+    return CORAL_OK;
+}
+
+// Test hook (not part of the declared ABI): index of the (device, metric, kernel variant) slot in
+// the per-device cache of granted shared-memory sizes, -1 when the device is not cached.
+int coral_internal_grant_slot(int device, int metric, int cluster) {
+    static int table[coral::kMaxGrantDevices * 4];
+    int* s = coral::granted_slot(table, device, metric, cluster != 0);
+    return s ? (int)(s - table) : -1;
+}
 int coral_compiled_sm(void) { return 100; }
 
 const char* coral_last_error(coral_index_t* h) { return h ? h->err.c_str() : g_create_error.c_str(); }

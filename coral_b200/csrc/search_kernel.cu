@@ -29,8 +29,11 @@
 // yields the same set; ties are resolved by id instead of by thread position.
 //
 // Nothing here traps or spins without bound: every mbarrier wait has a clock
-// limit after which an error flag is raised and the CTA stops taking queries.
+// limit after which an error flag is raised; once it is up every later wait returns at once and
+// no CTA (or cluster) takes another query.
 #include "search_kernel.cuh"
+
+#include <mutex>
 
 namespace coral {
 
@@ -72,6 +75,7 @@ struct Control {
     int beam_cnt;
     int fill;
     int status;
+    int abort;   // cluster mode: the leader saw the error flag; every CTA of the cluster stops after this query
     float worst;
     // per-query counters
     int n_dist, n_exp, n_scan, n_spill, hops, rounds, max_cand;
@@ -117,6 +121,9 @@ __device__ __forceinline__ uint32_t mbar_try_wait_parked(uint64_t* bar, uint32_t
 // polling, and the clock limit is only looked at every 64 wake-ups.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
     if (mbar_try_wait(bar, parity)) return true;
+    // A wait that already ran out anywhere in the grid invalidates the launch: later waits give up
+    // at once, so the kernel drains in the time of one limit instead of one limit per chunk.
+    if (*(volatile int*)err != 0) return false;
     const long long t0 = clock64();
     for (uint32_t spins = 1; !mbar_try_wait_parked(bar, parity, 4000u); ++spins) {
         if ((spins & 63u) == 0u && clock64() - t0 > kWaitClocks) {
@@ -373,6 +380,7 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
     int* p_exp_next = CLUSTER ? &GC->exp_next : &S.exp_next;
     int* p_cand_count = CLUSTER ? &GC->cand_count : &S.cand_count;
 
+    if (tid == 0) S.abort = 0;
     if (lane == 0)
         for (int s = 0; s < P.stages; ++s) mbar_init(&bars[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -409,7 +417,7 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
         if (tid == 0) {
             int q = -1;
             if (CLUSTER)
-                q = group + turn * n_groups;   // static: every CTA of the cluster must agree
+                q = S.abort ? -1 : group + turn * n_groups;   // static: every CTA of the cluster must agree
             else if (*(volatile int*)a.err_flag == 0)
                 q = atomicAdd(a.q_counter, 1);
             if (q < 0 || q >= a.Q) q = -1;
@@ -440,6 +448,14 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
         // ---------------------------------------------------------------- entry points
         for (int i = warp; leader && i < a.M; i += (nthreads >> 5)) {
             const int id = a.start_ids[i];
+            if (id < 0 || (int64_t)id >= a.n) {   // never dereferenced: the slot stays padding, the query is flagged
+                if (lane == 0) {
+                    atomicSub(&S.beam_cnt, 1);
+                    atomicSub(&S.n_dist, 1);
+                    atomicMax(&S.status, 4);
+                }
+                continue;
+            }
             if (lane == 0) {
                 const int r = visited_insert(shash, P.hs_bits, ghash, a.gh_mask, epoch, id, n_spill);
                 if (r == 2) overflow = true;  // duplicates are kept on purpose (src/search_gpu.cu:396-397)
@@ -906,6 +922,7 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
         if (__any_sync(0xffffffffu, overflow) && lane == 0) atomicMax(&S.status, 2);
         __syncthreads();
         if (CLUSTER) {   // fold the other CTAs' tallies into the leader's
+            if (leader && tid == 0) GC->abort = *(volatile int*)a.err_flag;
             if (!leader && tid == 0) {
                 atomicAdd(&GC->n_scan, S.n_scan);
                 atomicAdd(&GC->n_spill, S.n_spill);
@@ -923,6 +940,7 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
                 if (load_shared_int(&GC->status) == 2 && S.status < 2) S.status = 2;
                 GC->n_scan = GC->n_spill = GC->n_exp = GC->n_dist = GC->status = 0;
             }
+            if (tid == 0) S.abort = load_shared_int(&GC->abort);
             __syncthreads();
         }
 
@@ -952,6 +970,7 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
             if (lane == 0) {
                 int st = S.status;
                 if (st == 0 && cnt < a.L) st = 1;
+                if (a.worst_status && st != 0) atomicMax(a.worst_status, st);
                 if (a.stats_out) {
                     int32_t* o = a.stats_out + (size_t)qid * 8;
                     o[0] = st;
@@ -971,6 +990,11 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
 
 }  // namespace
 
+int* granted_slot(int* table, int device, int metric, bool cluster) {
+    if (device < 0 || device >= kMaxGrantDevices || metric < 0 || metric > 1) return nullptr;   // uncached: always set
+    return table + (device * 2 + metric) * 2 + (cluster ? 1 : 0);
+}
+
 namespace {
 template <int METRIC, bool CLUSTER>
 const void* kernel_ptr() {
@@ -982,15 +1006,25 @@ const void* kernel_for(int metric, bool cluster) {
 }
 // The opt-in shared-memory limit of each instantiation only ever grows, so plans made for other
 // beam capacities stay launchable.
+// The attribute belongs to the current device's context, so the cache is kept per device; a
+// mutex guards it because handles on different devices may be driven from different threads.
 bool grant_smem(int metric, bool cluster, int bytes) {
-    static int granted[2][2] = {{0, 0}, {0, 0}};
-    if (bytes <= granted[metric][cluster]) return true;
+    static std::mutex mu;
+    static int granted[kMaxGrantDevices][2][2] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    int* slot = granted_slot(&granted[0][0][0], dev, metric, cluster);
+    if (slot && bytes <= *slot) return true;
     if (cudaFuncSetAttribute(kernel_for(metric, cluster), cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) !=
         cudaSuccess) {
         cudaGetLastError();
         return false;
     }
-    granted[metric][cluster] = bytes;
+    if (slot) *slot = bytes;
     return true;
 }
 }  // namespace

@@ -35,7 +35,8 @@ struct ClusterCtl {
     int exp_count, exp_next, cand_count, done;
     float worst;
     int n_dist, n_exp, n_scan, n_spill, status;
-    int pad[6];
+    int abort;   // the leader saw the launch's error flag: the cluster takes no further query
+    int pad[5];
 };
 
 struct SearchArgs {
@@ -52,6 +53,7 @@ struct SearchArgs {
     uint64_t* gcand;           // [grid][cand_cap] candidates of the current round
     int* q_counter;            // next query to take
     int* err_flag;             // set when a bounded wait ran out
+    int* worst_status;         // nullable: atomicMax of the per-query status words of the launch
     long long* dbg;            // self-checking build only: [0] first failed check, [1..4] its values
     ClusterCtl* cctl;          // cluster mode: [clusters] round state
     int32_t* gexp;             // cluster mode: [clusters][L] ids to expand this round
@@ -65,6 +67,11 @@ struct SearchArgs {
     int max_rounds;
     SearchPlan plan;
 };
+
+// Cache of the opt-in shared-memory size granted per (device, metric, kernel variant): the slot of
+// a [kMaxGrantDevices][2][2] table, or nullptr for a device the table does not cover.
+constexpr int kMaxGrantDevices = 64;
+int* granted_slot(int* table, int device, int metric, bool cluster);
 
 // Launches the kernel for `metric` (0 = L2, 1 = IP) with `grid` CTAs on `stream`.  With
 // cluster_size > 1 the grid is made of thread-block clusters of that many CTAs, each cluster

@@ -28,6 +28,7 @@
 #include <mutex>
 
 #include "../../include/coral_b200.h"
+#include "plan.cuh"
 #include "search_kernel.cuh"
 
 namespace {
@@ -47,54 +48,20 @@ struct DeviceState {
     uint32_t epoch_base = 0;
     uint32_t last_entries = 0;  // carving of the previous call: a different one invalidates the tables
     int last_cand_cap = 0, last_grid = 0;
+    int last_status = 0;        // worst per-query status of the previous call
 };
 DeviceState g_state[kMaxDevices];
 std::mutex g_mutex;
 
-int next_pow2(int x) {
-    int p = 1;
-    while (p < x) p <<= 1;
-    return p;
-}
-int align_up(int x, int a) { return (x + a - 1) / a * a; }
-
-// One 256-byte stage per warp, four warps, no shared-memory visited table: the
-// shape the regular path defaults to.
-bool plan_for(int dim, int L, int smem_optin, coral::SearchPlan& p) {
-    const int row_bytes = dim * 4;
-    p = coral::SearchPlan{};
-    p.warps = 4;
-    int nc = (row_bytes + 255) / 256;
-    while (nc <= row_bytes / 16 && !(row_bytes % nc == 0 && (row_bytes / nc) % 16 == 0)) ++nc;
-    if (nc > row_bytes / 16) return false;
-    p.n_chunks = nc;
-    p.chunk_bytes = row_bytes / nc;
-    p.row_stride = p.chunk_bytes + (((p.chunk_bytes / 16) % 2 == 0) ? 16 : 0);
-    p.stage_bytes = 32 * p.row_stride;
-    p.stages = 1;
-    p.hs_bits = 0;
-    p.carry = 1;
-    p.LP = next_pow2(L > 32 ? L : 32);
-    int off = 0;
-    p.off_query = off;  off = align_up(off + dim * 4, 16);
-    p.off_beam0 = off;  off += p.LP * 8;
-    p.off_beam1 = off;  off += p.LP * 8;
-    p.off_exp = off;    off = align_up(off + L * 4, 16);
-    p.off_hash = off;
-    p.off_bar = off;    off += p.warps * 8 * 8;
-    p.off_pend = off;   off += p.warps * coral::kPendCap * 4;
-    p.off_bids = off;   off += p.warps * 64 * 4;
-    off = align_up(off, 128);
-    p.off_stage = off;
-    p.smem_bytes = off + p.warps * p.stage_bytes;
-    if (p.smem_bytes + 1024 > smem_optin) return false;
-    int per_sm = smem_optin / (p.smem_bytes + 1024);
-    p.ctas_per_sm = per_sm > 8 ? 8 : per_sm;
-    int tile = 64;
-    const int cap = p.warps * p.stage_bytes / 8 < 2048 ? p.warps * p.stage_bytes / 8 : 2048;
-    while (tile * 2 <= cap) tile <<= 1;
-    p.tile_max = tile;
-    return p.tile_max >= p.warps * 32;
+// cudaPointerGetAttributes allocates nothing; a host pointer handed in by mistake is refused here
+// instead of faulting in the kernel.
+bool is_device_ptr(const void* p) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
 }
 
 }  // namespace
@@ -114,6 +81,9 @@ extern "C" int coral_search_static(int device, void* stream, const float* d_vecs
     if ((long long)L * deg_pad > kMaxCandidates) return CORAL_ERR_LIMIT;
     if (Q > (1 << 24)) return CORAL_ERR_LIMIT;
     if (Q == 0) return CORAL_OK;
+    if (!is_device_ptr(d_vecs) || !is_device_ptr(d_adj) || !is_device_ptr(d_start_ids) || !is_device_ptr(d_queries) ||
+        !is_device_ptr(d_ids_out) || (d_dists_out && !is_device_ptr(d_dists_out)))
+        return CORAL_ERR_ARG;
 
     std::lock_guard<std::mutex> lock(g_mutex);
     if (cudaSetDevice(device) != cudaSuccess) {
@@ -140,22 +110,31 @@ extern "C" int coral_search_static(int device, void* stream, const float* d_vecs
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
+    // The same planner as the handle-based path, with its default options.
     coral::SearchPlan plan;
-    if (!plan_for(dim, L, ds.smem_optin, plan)) return CORAL_ERR_LIMIT;
+    const char* why = nullptr;
+    if (!coral::make_plan(dim, ds.smem_optin, coral::PlanOptions{}, L, plan, &why)) return CORAL_ERR_LIMIT;
     int per_sm = coral::beam_search_occupancy(plan, metric);
     if (per_sm <= 0) return CORAL_ERR_CUDA;
     if (per_sm > plan.ctas_per_sm) per_sm = plan.ctas_per_sm;
 
     // carve the array: [control words | per-CTA visited tables | per-CTA candidate buffers]
+    // The visited table gets 8 x L x deg_pad entries per CTA (what coral_search_prepare gives it)
+    // when a full grid of such CTAs fits the array, else 4 x (never fewer than 4096).
     const int cand_cap = L * deg_pad;
-    uint32_t gh_entries = 1u << 12;
-    while (gh_entries < 4u * (uint32_t)cand_cap) gh_entries <<= 1;
-    const size_t per_cta = (size_t)gh_entries * 8 + (size_t)cand_cap * 8;
-    size_t fit = (kStaticScratchBytes - kCtrlBytes) / per_cta;
-    if (fit < 1) return CORAL_ERR_LIMIT;
     int grid = ds.sm_count * per_sm;
-    if ((size_t)grid > fit) grid = (int)fit;
     if (grid > Q) grid = Q;
+    uint32_t gh_entries = 1u << 12;
+    while (gh_entries < 8u * (uint32_t)cand_cap) gh_entries <<= 1;
+    size_t per_cta = (size_t)gh_entries * 8 + (size_t)cand_cap * 8;
+    if ((size_t)grid * per_cta > kStaticScratchBytes - kCtrlBytes && gh_entries > (1u << 12) &&
+        gh_entries / 2 >= 4u * (uint32_t)cand_cap) {
+        gh_entries >>= 1;
+        per_cta = (size_t)gh_entries * 8 + (size_t)cand_cap * 8;
+    }
+    const size_t fit = (kStaticScratchBytes - kCtrlBytes) / per_cta;
+    if (fit < 1) return CORAL_ERR_LIMIT;
+    if ((size_t)grid > fit) grid = (int)fit;
 
     const bool recarved = gh_entries != ds.last_entries || cand_cap != ds.last_cand_cap || grid != ds.last_grid;
     ds.last_entries = gh_entries;
@@ -187,6 +166,7 @@ extern "C" int coral_search_static(int device, void* stream, const float* d_vecs
     a.stats_out = nullptr;
     a.q_counter = reinterpret_cast<int*>(ds.scratch);
     a.err_flag = reinterpret_cast<int*>(ds.scratch) + 1;
+    a.worst_status = reinterpret_cast<int*>(ds.scratch) + 4;
     a.hops_total = reinterpret_cast<unsigned long long*>(ds.scratch) + 1;
     a.ghash = reinterpret_cast<uint64_t*>(ds.scratch + kCtrlBytes);
     a.gcand = reinterpret_cast<uint64_t*>(ds.scratch + kCtrlBytes + (size_t)grid * gh_entries * 8);
@@ -209,11 +189,19 @@ extern "C" int coral_search_static(int device, void* stream, const float* d_vecs
     }
     ds.epoch_base += (uint32_t)Q;
 
-    int ctrl[2] = {0, 0};
+    int ctrl[5] = {0, 0, 0, 0, 0};   // query counter, error flag, hop total (2 words), worst per-query status
     if (cudaMemcpyAsync(ctrl, ds.scratch, sizeof(ctrl), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
         cudaStreamSynchronize(st) != cudaSuccess) {
         cudaGetLastError();
         return CORAL_ERR_CUDA;
     }
-    return ctrl[1] ? CORAL_ERR_KERNEL : CORAL_OK;
+    ds.last_status = ctrl[4];
+    if (ctrl[1]) return CORAL_ERR_KERNEL;
+    return ctrl[4] >= CORAL_Q_HASH_OVERFLOW ? CORAL_ERR_QUERY : CORAL_OK;
+}
+
+extern "C" int coral_search_static_status(int device) {
+    if (device < 0 || device >= kMaxDevices) return -1;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    return g_state[device].last_status;
 }

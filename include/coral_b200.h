@@ -37,12 +37,14 @@ extern "C" {
 #define CORAL_ERR_NOGPU 4    /* no usable CUDA device: there is no CPU fallback */
 #define CORAL_ERR_KERNEL 5   /* the kernel gave up on a bounded wait; results are invalid */
 #define CORAL_ERR_LIMIT 6    /* request exceeds what coral_search_prepare sized */
+#define CORAL_ERR_QUERY 7    /* results are in place, but some query ended with a per-query status >= 2 */
 
 /* per-query status written to stats[q][0] */
 #define CORAL_Q_OK 0
 #define CORAL_Q_BEAM_UNDERFULL 1  /* fewer than L nodes reachable (reference asserts, src/search_gpu.cu:444) */
 #define CORAL_Q_HASH_OVERFLOW 2   /* visited set outgrew its tables: result approximate */
 #define CORAL_Q_ROUND_LIMIT 3     /* stopped by the round bound */
+#define CORAL_Q_BAD_START 4       /* a start id outside [0, n) was skipped (never dereferenced) */
 
 /* stats row per query: status, n_dist, n_exp, rounds, hops, n_scan, max_cand, n_spill */
 #define CORAL_STATS_W 8
@@ -52,6 +54,14 @@ typedef struct coral_index coral_index_t;
 /* Library version and the SM architecture the kernels were compiled for (100). */
 int coral_version(void);
 int coral_compiled_sm(void);
+
+/* The kernel's automatic shared-memory plan for vectors of `dim` floats and beam
+ * capacity L on a device with `smem_optin_bytes` of opt-in shared memory per CTA
+ * (232448 on B200): out8 = warps per CTA, CTAs per SM, bytes per row chunk, chunks
+ * per row, stage buffers per warp, dynamic shared memory per CTA, candidate sort
+ * tile, beam array length.  Pure host arithmetic (no device needed).  Replaces the
+ * launch-shape arithmetic at src/search_gpu.cu:859-860. */
+int coral_plan(int dim, int L, int smem_optin_bytes, int* out8);
 
 /* Replaces the GPU branch of Graph::Graph (include/graph.cuh:222-266) and
  * GPUFuncs::GPUFuncs (src/gpufuncs.cu:70-118): binds a handle to `device`
@@ -192,16 +202,27 @@ int coral_map_ids(coral_index_t* h, int32_t* d_ids, int64_t count, const int32_t
  * Same kernel and same results as coral_search, but the kernel's scratch (visited
  * table, candidate buffers) lives in a 64 MiB array inside the library image, so
  * this function calls no cudaMalloc/cudaFree and builds no host containers.
- * Every pointer is a device pointer owned by the caller; adjacency is the padded
- * layout [n][deg_pad].  Limits: L * deg_pad <= 16384 (CORAL_ERR_LIMIT beyond),
- * Q <= 2^24.  The first call on a device resolves the array's address: make it
- * before any stream capture.  All calls share the array, which keeps the last
- * call's contents (control words are re-zeroed, table entries are epoch-tagged);
- * calls that overlap on one GPU race.  Runs on `stream` and returns after
- * synchronising it. */
+ * Every pointer is a device pointer owned by the caller (a host pointer is
+ * CORAL_ERR_ARG); adjacency is the padded layout [n][deg_pad].  Limits:
+ * L * deg_pad <= 16384 (CORAL_ERR_LIMIT beyond), Q <= 2^24.  The first call on a
+ * device resolves the array's address: make it before any stream capture.  All
+ * calls share the array, which keeps the last call's contents (control words are
+ * re-zeroed, table entries are epoch-tagged); calls that overlap on one GPU race.
+ * Runs on `stream` and returns after synchronising it.
+ * Differences from coral_search: there is no per-query stats array; instead the
+ * worst per-query status of the call is kept (coral_search_static_status), and a
+ * call in which some query ended with status >= CORAL_Q_HASH_OVERFLOW returns
+ * CORAL_ERR_QUERY with the results in place.  A start id outside [0, n) is
+ * skipped, never dereferenced (CORAL_Q_BAD_START).  The visited table per CTA has
+ * 8 x L x deg_pad entries, as on the regular path, when a full grid fits the
+ * array, else 4 x. */
 int coral_search_static(int device, void* stream, const float* d_vecs, const int32_t* d_adj, int64_t n,
                         int dim, int deg_pad, int metric, const int32_t* d_start_ids, int M,
                         const float* d_queries, int Q, int L, int k, int32_t* d_ids_out, float* d_dists_out);
+
+/* Worst per-query status (CORAL_Q_*) of the last coral_search_static call on
+ * `device`; -1 for a device index out of range.  No counterpart in the reference. */
+int coral_search_static_status(int device);
 
 /* Last error text of the handle (or of handle creation when h is NULL). */
 const char* coral_last_error(coral_index_t* h);

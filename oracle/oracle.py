@@ -4,7 +4,9 @@ Only tests, the smoke check and the benchmark's baseline legs may import this
 module.  ``liboracle.so`` holds the restatement of the reference GPU kernel's
 semantics (``beam_search_oracle.c``) and the self-contained CPU best-first port
 (``search_in_cpu_port.c``); ``_ref/libref_cpu.so`` is the same best-first loop
-driving the reference's own queue and AVX-512 distance classes.
+driving the reference's own queue and AVX-512 distance classes;
+``_ref/libref_gpu.so`` is the reference's own search launcher and kernel, compiled
+unmodified from the reference tree for sm_100a (``ref_gpu_driver.cu``).
 """
 from __future__ import annotations
 
@@ -21,11 +23,22 @@ STAT_NAMES = ("status", "n_dist", "n_exp", "rounds", "hops", "n_scan", "max_cand
 
 _lib = None
 _ref = None
+_ref_gpu = None
+
+
+def reference_dir() -> str:
+    """Where the reference tree lies: $CORAL_REFERENCE_DIR, else a directory named
+    ``reference`` beside the repository; '' when neither exists."""
+    cand = os.environ.get("CORAL_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "include", "efanna2e")) else ""
 
 
 def build(quiet: bool = True) -> None:
     """Compile the checkers (and ``_ref`` when the reference tree is present)."""
-    subprocess.run(["make", "-C", _HERE], check=True,
+    env = dict(os.environ, CORAL_REFERENCE_DIR=reference_dir())
+    for var in ("CC", "CXX"):
+        env.pop(var, None)
+    subprocess.run(["make", "-C", _HERE], check=True, env=env,
                    stdout=subprocess.DEVNULL if quiet else None)
 
 
@@ -205,3 +218,41 @@ def cpu_search(base, adj, start_ids, queries, L, k, threads=0, prefer_reference=
     if rc != 0:
         raise ValueError("coral_cpu_search: bad arguments")
     return ids, dists, int(hops.value), float(secs.value), kind, threads
+
+
+def have_ref_gpu() -> bool:
+    return os.path.exists(os.path.join(_HERE, "_ref", "libref_gpu.so"))
+
+
+def ref_gpu_search(base, adj, start_ids, queries, L, k, metric, max_degree=None):
+    """The reference's own GPUFuncs::search_gpu + beam_search_kernel (bitset overload) on the
+    current CUDA device.  Every query must fill its beam (oracle status 0): the reference
+    kernel reads out of range otherwise.  Returns (ids, dists, total_hops, seconds)."""
+    global _ref_gpu
+    if _ref_gpu is None:
+        _ref_gpu = C.CDLL(os.path.join(_HERE, "_ref", "libref_gpu.so"))
+        f32p, i32p = C.POINTER(C.c_float), C.POINTER(C.c_int32)
+        _ref_gpu.coral_ref_gpu_search.restype = C.c_int
+        _ref_gpu.coral_ref_gpu_search.argtypes = [
+            f32p, C.c_int64, C.c_int, i32p, C.c_int, C.c_int, C.c_int, i32p, C.c_int, f32p, C.c_int,
+            C.c_int, C.c_int, i32p, f32p, C.POINTER(C.c_int64), C.POINTER(C.c_double)]
+    base, bp = _f32(base)
+    adj, ap = _i32(adj)
+    start_ids, sp = _i32(start_ids)
+    queries, qp = _f32(queries)
+    n, dim = base.shape
+    Q = queries.shape[0]
+    if max_degree is None:
+        max_degree = int((adj >= 0).sum(1).max())
+    ids = np.empty((Q, k), np.int32)
+    dists = np.empty((Q, k), np.float32)
+    hops = C.c_int64(0)
+    secs = C.c_double(0.0)
+    rc = _ref_gpu.coral_ref_gpu_search(bp, n, dim, ap, adj.shape[1], max_degree, metric_id(metric), sp,
+                                       len(start_ids), qp, Q, L, k,
+                                       ids.ctypes.data_as(C.POINTER(C.c_int32)),
+                                       dists.ctypes.data_as(C.POINTER(C.c_float)),
+                                       C.byref(hops), C.byref(secs))
+    if rc != 0:
+        raise RuntimeError(f"coral_ref_gpu_search failed with {rc}")
+    return ids, dists, int(hops.value), float(secs.value)

@@ -46,3 +46,32 @@ def test_product_code_never_touches_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
                 src = open(os.path.join(base, f), errors="ignore").read()
                 assert "oracle" not in src.lower(), f"{f} mentions the oracle"
+
+
+def test_planner_is_host_arithmetic_and_matches_the_documented_plans():
+    lib = capi.load()
+    out = (ctypes.c_int * 8)()
+    smem = 232448   # opt-in shared memory per CTA on B200
+    assert lib.coral_plan(512, 64, smem, out) == capi.OK
+    warps, ctas, chunk, n_chunks, stages, smem_bytes, tile, LP = list(out)
+    assert chunk * n_chunks == 512 * 4 and chunk == 256 and stages == 1 and LP == 64
+    assert warps * ctas == 20 and ctas * (smem_bytes + 1024) <= smem    # 5 CTAs x 4 warps per SM
+    assert lib.coral_plan(200, 64, smem, out) == capi.OK                  # 800-byte rows: 400-byte chunks
+    assert out[2] == 400 and out[3] == 2 and out[1] >= 5
+    assert lib.coral_plan(200, 512, smem, out) == capi.OK                 # only four CTAs fit: 160-byte chunks
+    assert out[2] == 160 and out[3] == 5
+    assert lib.coral_plan(6, 64, smem, out) == capi.ERR_ARG               # dim % 4
+    assert lib.coral_plan(512, 64, 4096, out) == capi.ERR_LIMIT           # nothing fits 4 KB
+
+
+def test_granted_shared_memory_is_cached_per_device():
+    lib = capi.load()
+    slot = lib.coral_internal_grant_slot
+    seen = set()
+    for dev in (0, 1, 7, 63):
+        for metric in (0, 1):
+            for cluster in (0, 1):
+                s = slot(dev, metric, cluster)
+                assert s >= 0 and s not in seen, "two (device, metric, variant) triples share a cache slot"
+                seen.add(s)
+    assert slot(64, 0, 0) == -1 and slot(-1, 0, 0) == -1   # uncached devices always set the attribute

@@ -29,7 +29,7 @@ def full():
     ix.attach_vectors(ds.base)
     ix.set_adjacency(g.adj)
     ix.set_start_ids(g.start_ids)
-    ix.prepare(Q, L, K)
+    ix.prepare(Q, 256, K)
     ids, d, st, hops = ix.search(ds.test, L, K, dists=True, stats=True)
     to_np = lambda x: x.cpu().numpy() if hasattr(x, "cpu") else np.asarray(x)
     yield dict(ds=ds, g=g, ix=ix, ids=to_np(ids), d=to_np(d), st=to_np(st), hops=hops, to_np=to_np, torch=torch, synth=synth)
@@ -90,13 +90,57 @@ def test_recall_against_exact_search(full):
     assert hit / (K * n_gt) >= 0.95
 
 
-def test_oracle_parity_on_a_handful_of_the_queries(full):
+@pytest.fixture(scope="module")
+def host_copy(full):
+    """The index on the host, for the oracle (20 GB of vectors: copied once per module)."""
     ds, g = full["ds"], full["g"]
-    base = ds.base.cpu().numpy()
-    adj = g.adj.cpu().numpy()
-    rows = [0, 1, 2, 3, 49_999, 50_000, 99_998, 99_999]
-    qs = ds.test.cpu().numpy()[rows]
-    ref_ids, ref_d, ref_st = oracle.search(base, adj, g.start_ids.cpu().numpy(), qs, L, K, "ip")
-    assert np.array_equal(full["ids"][rows], ref_ids)
-    assert np.array_equal(full["d"][rows].view(np.uint32), ref_d.view(np.uint32))
-    assert np.array_equal(full["st"][rows][:, :7], ref_st[:, :7])
+    return dict(base=ds.base.cpu().numpy(), adj=g.adj.cpu().numpy(), start=g.start_ids.cpu().numpy(),
+                test=ds.test.cpu().numpy())
+
+
+def test_oracle_parity_on_a_thousand_queries_at_every_configured_L(full, host_copy):
+    """BASELINE config 3: L in {64, 128, 256}, k = 10 -- ids, distance bits and the seven counters of
+    1000 queries spread over the batch must equal the oracle's."""
+    ix, ds, to_np = full["ix"], full["ds"], full["to_np"]
+    rows = np.unique(np.concatenate([np.arange(0, Q, Q // 1000)[:1000], [Q - 1]]))
+    qs = host_copy["test"][rows]
+    for L_ in (64, 128, 256):
+        ref_ids, ref_d, ref_st = oracle.search(host_copy["base"], host_copy["adj"], host_copy["start"], qs, L_, K, "ip")
+        if L_ == L:
+            ids, d, st = full["ids"], full["d"], full["st"]
+        else:
+            ids, d, st, _ = ix.search(ds.test, L_, K, dists=True, stats=True)
+            ids, d, st = to_np(ids), to_np(d), to_np(st)
+        assert np.array_equal(ids[rows], ref_ids), f"L={L_}: ids differ"
+        assert np.array_equal(d[rows].view(np.uint32), ref_d.view(np.uint32)), f"L={L_}: distance bits differ"
+        assert np.array_equal(st[rows][:, :7], ref_st[:, :7]), f"L={L_}: counters differ"
+
+
+def test_small_batches_with_and_without_deleted_points(full, host_copy):
+    """BASELINE config 5, first leg: batches of 1, 8, 64 and 512 queries at L = 128, k = 10, and the same
+    with 10 % of the points marked deleted (src/search_gpu.cu:716: hidden from the top-k, still
+    traversed).  Oracle parity on every query of every batch; deleted: the oracle's beam (k = L) with
+    the deleted ids dropped."""
+    ix, ds, to_np = full["ix"], full["ds"], full["to_np"]
+    L_ = 128
+    rng = np.random.default_rng(77)
+    dead = rng.random(N) < 0.10
+    bits = np.packbits(dead, bitorder="little")
+    bits = np.concatenate([bits, np.zeros((-len(bits)) % 4, np.uint8)]).view(np.uint32)
+    lo = 0
+    for B in (1, 8, 64, 512):
+        qs = host_copy["test"][lo:lo + B]
+        ref_ids, ref_d, ref_st = oracle.search(host_copy["base"], host_copy["adj"], host_copy["start"], qs, L_, L_, "ip")
+        ids, d, st, _ = ix.search(ds.test[lo:lo + B], L_, K, dists=True, stats=True)
+        assert np.array_equal(to_np(ids), ref_ids[:, :K]) and np.array_equal(to_np(st)[:, :7], ref_st[:, :7])
+        assert np.array_equal(to_np(d).view(np.uint32), ref_d[:, :K].view(np.uint32))
+        ix.set_deleted(bits)
+        ids_d, d_d, st_d, _ = ix.search(ds.test[lo:lo + B], L_, K, dists=True, stats=True)
+        ix.set_deleted(None)
+        ids_d, d_d = to_np(ids_d), to_np(d_d)
+        for r in range(B):
+            alive = ~dead[ref_ids[r]]
+            assert np.array_equal(ids_d[r], ref_ids[r][alive][:K])
+            assert np.array_equal(d_d[r].view(np.uint32), ref_d[r][alive][:K].view(np.uint32))
+        assert np.array_equal(to_np(st_d)[:, 1:7], ref_st[:, 1:7])
+        lo += B

@@ -45,10 +45,17 @@ def test_static_entry_point_matches_regular_entry_point(metric):
     tv, ta = torch.from_numpy(c.base).cuda(), torch.from_numpy(c.adj).cuda()
     ts, tq = torch.from_numpy(c.start).cuda(), torch.from_numpy(c.queries).cuda()
     m = capi.L2 if metric == "l2" else capi.IP
+    _static_search(lib, tv, ta, ts, tq, c.n, c.dim, c.adj.shape[1], m, 64, 10)   # first call: address look-up
     for L in (64, 128, 64):       # consecutive calls share the scratch array, with and without re-carving
         for _ in range(2):
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
             rc, ids, dists = _static_search(lib, tv, ta, ts, tq, c.n, c.dim, c.adj.shape[1], m, L, 10)
+            # the output tensors come from torch's cache or the driver; the call itself must not
+            # take device memory: what is free afterwards is what was free before minus those two
+            assert torch.cuda.mem_get_info()[0] >= free_before - 2 * (1 << 21)
             assert rc == capi.OK
+            assert lib.coral_search_static_status(0) == 0
             assert np.array_equal(ids, want[L][0])
             assert np.array_equal(dists.view(np.uint32), want[L][1].view(np.uint32))   # bit-exact, like the other tests
 
@@ -65,3 +72,26 @@ def test_static_entry_point_rejects_what_does_not_fit():
     assert rc == capi.ERR_ARG
     rc, ids, _ = _static_search(lib, tv, ta, ts, tq, c.n, c.dim, 32, capi.L2, 64, 10)   # still usable
     assert rc == capi.OK and (ids >= 0).all()
+
+
+def test_static_entry_point_reports_query_status_and_refuses_bad_pointers():
+    import torch
+    lib = capi.load()
+    c = cases.chain_case()            # ten reachable nodes: every beam ends under-full (status 1)
+    tv, ta = torch.from_numpy(c.base).cuda(), torch.from_numpy(c.adj).cuda()
+    ts, tq = torch.from_numpy(c.start).cuda(), torch.from_numpy(c.queries).cuda()
+    rc, ids, _ = _static_search(lib, tv, ta, ts, tq, c.n, c.dim, 32, capi.L2, 64, 16)
+    assert rc == capi.OK and lib.coral_search_static_status(0) == 1
+    assert (ids[:, :10] >= 0).all() and (ids[:, 10:] == -1).all()
+    # a start id outside [0, n) is skipped and flagged, never dereferenced
+    bad = torch.tensor([0, c.n + 5, -3], dtype=torch.int32, device="cuda")
+    rc, ids2, _ = _static_search(lib, tv, ta, bad, tq, c.n, c.dim, 32, capi.L2, 64, 16)
+    assert rc == capi.ERR_QUERY and lib.coral_search_static_status(0) == 4
+    assert np.array_equal(ids2, ids)
+    # a host pointer handed in by mistake is an argument error, not a fault
+    host_q = np.ascontiguousarray(c.queries)
+    out = torch.empty((len(host_q), 16), dtype=torch.int32, device="cuda")
+    rc = lib.coral_search_static(0, None, C.c_void_p(tv.data_ptr()), C.c_void_p(ta.data_ptr()), c.n, c.dim, 32,
+                                 capi.L2, C.c_void_p(ts.data_ptr()), 1, C.c_void_p(host_q.ctypes.data),
+                                 len(host_q), 64, 16, C.c_void_p(out.data_ptr()), None)
+    assert rc == capi.ERR_ARG
