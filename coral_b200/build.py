@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libcoral_b200.so")
 LIB_CHECKED = os.path.join(LIB_DIR, "libcoral_b200_checked.so")
-SOURCES = ["search_kernel.cu", "plan.cu", "schedule.cu", "capi.cu", "search_static.cu", "start_select.cu"]
+SOURCES = ["search_kernel.cu", "plan.cu", "dense_topk.cu", "schedule.cu", "capi.cu", "search_static.cu", "start_select.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared"]
 

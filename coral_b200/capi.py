@@ -25,7 +25,8 @@ EXPORTS = (
     "coral_index_set_deleted",
     "coral_search_prepare", "coral_search_free", "coral_search", "coral_search_async",
     "coral_search_check", "coral_last_kernel_ms", "coral_last_total_ms", "coral_launch_count",
-    "coral_set_option", "coral_get_option", "coral_count_hits", "coral_merge_shards",
+    "coral_set_option", "coral_get_option", "coral_count_hits", "coral_exact_knn", "coral_last_dense_ms",
+    "coral_last_dense_flops", "coral_merge_shards",
     "coral_map_ids", "coral_last_error", "coral_search_static", "coral_search_static_status",
 )
 
@@ -74,6 +75,9 @@ def load():
         "coral_set_option": (C.c_int, [vp, C.c_char_p, C.c_int]),
         "coral_get_option": (C.c_int, [vp, C.c_char_p, C.POINTER(C.c_int)]),
         "coral_count_hits": (C.c_int, [vp, i32p, i32p, C.c_int, C.c_int, C.c_int, i64p]),
+        "coral_exact_knn": (C.c_int, [vp, f32p, C.c_int, C.c_int, i32p, f32p, i64p]),
+        "coral_last_dense_ms": (C.c_float, [vp]),
+        "coral_last_dense_flops": (C.c_double, [vp]),
         "coral_merge_shards": (C.c_int, [vp, i32p, f32p, C.c_int, C.c_int, C.c_int, i32p, f32p, vp]),
         "coral_map_ids": (C.c_int, [vp, i32p, C.c_int64, i32p, vp]),
         "coral_last_error": (C.c_char_p, [vp]),
@@ -266,6 +270,33 @@ class Index:
         hits = C.c_int64(0)
         self._check(self._lib.coral_count_hits(self._h, rp, gp, int(rk.shape[0]), k, int(gk.shape[1]), C.byref(hits)))
         return int(hits.value)
+
+    def exact_knn(self, queries, k: int, dists: bool = True):
+        """Exact k nearest of the handle's vectors.  Host numpy in -> numpy out, CUDA tensor in -> CUDA
+        tensors out.  Returns (ids[Q,k], dists[Q,k] | None, number of uncertified queries)."""
+        bad = C.c_int64(0)
+        if _is_torch(queries) and queries.is_cuda:
+            import torch
+            q = queries.to(torch.float32).contiguous()
+            torch.cuda.current_stream(q.device).synchronize()
+            ids = torch.empty((q.shape[0], k), dtype=torch.int32, device=q.device)
+            dd = torch.empty((q.shape[0], k), dtype=torch.float32, device=q.device) if dists else None
+            self._check(self._lib.coral_exact_knn(self._h, C.c_void_p(q.data_ptr()), int(q.shape[0]), k,
+                                                  C.c_void_p(ids.data_ptr()),
+                                                  C.c_void_p(dd.data_ptr()) if dists else None, C.byref(bad)))
+            return ids, dd, int(bad.value)
+        q = np.ascontiguousarray(queries, dtype=np.float32)
+        ids = np.empty((q.shape[0], k), np.int32)
+        dd = np.empty((q.shape[0], k), np.float32) if dists else None
+        self._check(self._lib.coral_exact_knn(self._h, C.c_void_p(q.ctypes.data), int(q.shape[0]), k,
+                                              C.c_void_p(ids.ctypes.data),
+                                              C.c_void_p(dd.ctypes.data) if dists else None, C.byref(bad)))
+        return ids, dd, int(bad.value)
+
+    @property
+    def last_dense_tflops(self) -> float:
+        ms = float(self._lib.coral_last_dense_ms(self._h))
+        return float(self._lib.coral_last_dense_flops(self._h)) / (ms * 1e-3) / 1e12 if ms > 0 else 0.0
 
     def merge_shards(self, d_ids, d_dists, stream=None):
         """d_ids/d_dists: CUDA tensors [G,Q,k] -> merged CUDA tensors ([Q,k], [Q,k])."""

@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "../../include/coral_b200.h"
+#include "dense_topk.cuh"
 #include "plan.cuh"
 #include "schedule.cuh"
 #include "search_kernel.cuh"
@@ -49,6 +50,7 @@ struct Options {
     int probe_carry = 1;   // carry ids the first probe pair leaves open into the next scout step (0 = settle them at once)
     int gather = 0;        // row chunks to shared memory: 0 = one bulk copy per row chunk, 1 = 16-byte unit copies
     int schedule = 0;      // order large batches for L2 locality: 0 = automatic (batches >= 8192), 1 = always, -1 = never
+    int dense_passes = 3;  // tf32 passes of the dense scans behind coral_exact_knn: 3 = fp32-grade, 1 = plain tf32
 };
 
 }  // namespace
@@ -101,6 +103,12 @@ struct coral_index {
     unsigned long long* h_ctrl = nullptr;  // pinned mirror
     int64_t* d_hits = nullptr;
     std::map<int, std::pair<SearchPlan, int>> plans;  // L -> (plan, CTAs per SM)
+
+    // dense tensor-core scans (exact k-NN): workspace kept between calls
+    void* d_dense = nullptr;
+    size_t dense_bytes = 0;
+    float last_dense_ms = 0.f;
+    double last_dense_flops = 0.0;
 
     float last_kernel_ms = 0.f, last_total_ms = 0.f;
     int64_t launches = 0;
@@ -385,6 +393,7 @@ int coral_index_destroy(coral_index_t* h) {
     cudaFree(h->d_front_norm);
     cudaFree(h->d_ctrl);
     cudaFree(h->d_hits);
+    cudaFree(h->d_dense);
     if (h->h_ctrl) cudaFreeHost(h->h_ctrl);
     if (h->ev_t0) cudaEventDestroy(h->ev_t0);
     if (h->ev_k0) cudaEventDestroy(h->ev_k0);
@@ -521,6 +530,7 @@ int coral_set_option(coral_index_t* h, const char* name, int value) {
     else if (s == "visit_cache_bits") o.visit_cache_bits = value;
     else if (s == "gather") o.gather = value;
     else if (s == "probe_carry") o.probe_carry = value;
+    else if (s == "dense_passes") o.dense_passes = value;
     else return fail(h, CORAL_ERR_ARG, "unknown option " + s);
     h->plans.clear();
     return CORAL_OK;
@@ -543,6 +553,7 @@ int coral_get_option(coral_index_t* h, const char* name, int* value) {
     else if (s == "schedule") *value = o.schedule;
     else if (s == "gather") *value = o.gather;
     else if (s == "probe_carry") *value = o.probe_carry;
+    else if (s == "dense_passes") *value = o.dense_passes;
     else if (s == "sort_tile") *value = o.sort_tile;
     else if (s == "scout_ids") *value = o.scout_ids;
     else if (s == "visit_cache_bits") *value = o.visit_cache_bits;
@@ -844,6 +855,104 @@ int coral_count_hits(coral_index_t* h, const int32_t* res, const int32_t* gt, in
     cudaFree(d_gt);
     return rc;
 }
+
+// Exact k-NN of `Q` queries over `n_rows` rows at d_rows (device), ids relative to d_rows.
+static int exact_knn_over(coral_index* h, const float* d_rows, int64_t n_rows, const float* queries, int Q, int k,
+                          int passes, int32_t* ids_out, float* dists_out, int64_t* uncertified_out) {
+    if (k <= 0 || (int64_t)k > n_rows) return fail(h, CORAL_ERR_ARG, "exact knn: need 0 < k <= number of rows");
+    int keep = k + 28;                                   // slack between the selection and the k that are returned
+    if (keep > coral::kDenseMaxKeep) keep = coral::kDenseMaxKeep;
+    if (k > keep) return fail(h, CORAL_ERR_LIMIT, "exact knn: k must not exceed 256");
+    if (uncertified_out) *uncertified_out = 0;
+    if (Q == 0) return CORAL_OK;
+    cudaStream_t st = h->stream;
+    const int q_chunk = h->sm_count * coral::kDenseTileM;          // one CTA per SM and query tile
+    const int q_cap = std::min(Q, q_chunk);
+    const int q_tiles = (q_cap + coral::kDenseTileM - 1) / coral::kDenseTileM;
+    // base rows per scan launch: bounded by 2 GiB of split operands
+    int64_t b_cap = std::min<int64_t>(n_rows, std::max<int64_t>(coral::kDenseTileN, ((int64_t)1 << 28) / h->dim));
+    const int col_tiles = (int)((b_cap + coral::kDenseTileN - 1) / coral::kDenseTileN);
+    int n_split = std::max(1, std::min(std::min(coral::kDenseMaxSplit, h->sm_count / q_tiles), col_tiles));
+    const size_t need = coral::dense_workspace_bytes(q_cap, (int)b_cap, h->dim, n_split);
+    if (need > h->dense_bytes) {
+        cudaFree(h->d_dense);
+        h->d_dense = nullptr;
+        h->dense_bytes = 0;
+        CK(cudaMalloc(&h->d_dense, need));
+        h->dense_bytes = need;
+    }
+    coral::DenseWorkspace w;
+    coral::dense_workspace_carve(h->d_dense, q_cap, (int)b_cap, h->dim, n_split, w);
+    const bool q_dev = is_device_ptr(queries), i_dev = is_device_ptr(ids_out);
+    const bool d_dev = dists_out && is_device_ptr(dists_out);
+    float* dq = nullptr;
+    int32_t* di = nullptr;
+    float* dd = nullptr;
+    int32_t* d_cert = nullptr;
+    if (!q_dev) CK(cudaMalloc(&dq, (size_t)q_cap * h->dim * sizeof(float)));
+    if (!i_dev) CK(cudaMalloc(&di, (size_t)q_cap * k * sizeof(int32_t)));
+    if (dists_out && !d_dev) CK(cudaMalloc(&dd, (size_t)q_cap * k * sizeof(float)));
+    int rc = CORAL_OK;
+    int64_t bad = 0;
+    cudaError_t e = cudaEventRecord(h->ev_k0, st);
+    for (int q0 = 0; q0 < Q && e == cudaSuccess; q0 += q_cap) {
+        const int nq = std::min(q_cap, Q - q0);
+        const float* qsrc = queries + (size_t)q0 * h->dim;
+        if (!q_dev) {
+            e = cudaMemcpyAsync(dq, qsrc, (size_t)nq * h->dim * sizeof(float), cudaMemcpyHostToDevice, st);
+            qsrc = dq;
+        }
+        if (e == cudaSuccess) e = coral::dense_begin(w, qsrc, nq, h->dim, st, &h->launches);
+        for (int64_t r0 = 0; r0 < n_rows && e == cudaSuccess; r0 += b_cap) {
+            const int nr = (int)std::min<int64_t>(b_cap, n_rows - r0);
+            e = coral::dense_scan_chunk(w, qsrc, nq, d_rows + (size_t)r0 * h->dim, r0, nr, h->dim, h->metric, passes, keep,
+                                        h->sm_count, st, &h->launches);
+        }
+        int32_t* io = i_dev ? ids_out + (size_t)q0 * k : di;
+        float* dox = dists_out ? (d_dev ? dists_out + (size_t)q0 * k : dd) : nullptr;
+        if (e == cudaSuccess)
+            e = coral::dense_finish(w, qsrc, nq, d_rows, h->dim, h->metric, passes, keep, k, io, dox, d_cert, st, &h->launches);
+        int flags[4] = {0, 0, 0, 0};
+        if (e == cudaSuccess) e = cudaMemcpyAsync(flags, w.err, sizeof flags, cudaMemcpyDeviceToHost, st);
+        if (e == cudaSuccess && !i_dev)
+            e = cudaMemcpyAsync(ids_out + (size_t)q0 * k, di, (size_t)nq * k * sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+        if (e == cudaSuccess && dists_out && !d_dev)
+            e = cudaMemcpyAsync(dists_out + (size_t)q0 * k, dd, (size_t)nq * k * sizeof(float), cudaMemcpyDeviceToHost, st);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+        if (e == cudaSuccess && flags[0]) {
+            rc = fail(h, CORAL_ERR_KERNEL, "a bounded wait in the dense scan kernel ran out; results are invalid");
+            break;
+        }
+        bad += flags[1];
+    }
+    if (e == cudaSuccess && rc == CORAL_OK) {
+        e = cudaEventRecord(h->ev_k1, st);
+        if (e == cudaSuccess) e = cudaEventSynchronize(h->ev_k1);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&h->last_dense_ms, h->ev_k0, h->ev_k1);
+        h->last_dense_flops = 2.0 * (passes == 1 ? 1.0 : 3.0) * (double)Q * (double)n_rows * (double)h->dim;
+    }
+    cudaFree(dq);
+    cudaFree(di);
+    cudaFree(dd);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(h, CORAL_ERR_CUDA, std::string("exact knn: ") + cudaGetErrorString(e));
+    }
+    if (uncertified_out) *uncertified_out = bad;
+    return rc;
+}
+
+int coral_exact_knn(coral_index_t* h, const float* queries, int Q, int k, int32_t* ids_out, float* dists_out,
+                    int64_t* uncertified_out) {
+    if (!h || Q < 0 || (Q > 0 && (!queries || !ids_out))) return fail(h, CORAL_ERR_ARG, "null argument");
+    if (!h->d_vecs) return fail(h, CORAL_ERR_STATE, "exact knn: no vectors set");
+    if (int rc = ensure_device(h)) return rc;
+    return exact_knn_over(h, h->d_vecs, h->n, queries, Q, k, h->opt.dense_passes == 1 ? 1 : 3, ids_out, dists_out,
+                          uncertified_out);
+}
+
+float coral_last_dense_ms(coral_index_t* h) { return h ? h->last_dense_ms : 0.f; }
+double coral_last_dense_flops(coral_index_t* h) { return h ? h->last_dense_flops : 0.0; }
 
 int coral_merge_shards(coral_index_t* h, const int32_t* d_ids, const float* d_dists, int G, int Q, int k,
                        int32_t* d_ids_out, float* d_dists_out, void* stream) {

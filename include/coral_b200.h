@@ -167,6 +167,7 @@ int64_t coral_launch_count(coral_index_t* h);
  *   "max_rounds"             per-query round limit (status 3 when reached)
  *   "cluster_size"           CTAs that share one query when the batch is far smaller than the GPU:
  *                            0 = automatic, 1 = never, 2/4/8/16 = forced
+ *   "dense_passes"           tf32 passes of coral_exact_knn's selection scans: 3 (default) or 1
  *   "schedule"               run large batches grouped by the entry points' neighbour each query is
  *                            closest to, for L2 locality: 0 = automatic for batches >= 8192,
  *                            1 = always, -1 = never
@@ -183,6 +184,26 @@ int coral_get_option(coral_index_t* h, const char* name, int* value);
  * pointers. */
 int coral_count_hits(coral_index_t* h, const int32_t* res, const int32_t* gt, int Q, int k,
                      int gt_dim, int64_t* hits_out);
+
+/* Replaces the exhaustive Faiss flat search the reference calls for the k_b nearest
+ * base points of its training queries (src/knn.cu:174-193, include/myfaiss.h:17-29)
+ * and for ground truth (tests/comp_gt.cpp:121-155): the k closest of the handle's
+ * vectors for each of Q queries, closest first, ties by the smaller id.  The scores
+ * are formed on the tensor cores (tcgen05, tf32 operands split into high and low
+ * parts, three passes: fp32-grade) and only SELECT the k + 28 best per query; those
+ * are re-ranked with the exact fp32 distance in the order of the reference's device
+ * functions (include/utils.cuh:254-275, :307-323), which is also what dists_out
+ * (nullable) receives.  A query is certified when its exact k-th distance beats the
+ * best score an unselected row could have; *uncertified_out (nullable) counts the
+ * others (their answer is almost surely right, but not proven).  k <= 228.  Host or
+ * device pointers.  Option "dense_passes" = 1 selects with one plain tf32 pass. */
+int coral_exact_knn(coral_index_t* h, const float* queries, int Q, int k, int32_t* ids_out,
+                    float* dists_out, int64_t* uncertified_out);
+
+/* Device time (ms) and tensor-core floating-point operations (2 x passes x Q x n x dim)
+ * of the last coral_exact_knn call: selection scans and re-rank. */
+float coral_last_dense_ms(coral_index_t* h);
+double coral_last_dense_flops(coral_index_t* h);
 
 /* Shard merge (no counterpart in the reference, which is single-GPU): ids and
  * dists hold G per-shard results [G][Q][k] (global ids, -1 = padding); writes

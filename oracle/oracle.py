@@ -62,6 +62,8 @@ def _load():
         _lib.coral_oracle_merge_shards.argtypes = [i32p, f32p, C.c_int, C.c_int, C.c_int, C.c_int, i32p, f32p]
         _lib.coral_oracle_select_start_ids.restype = C.c_int
         _lib.coral_oracle_select_start_ids.argtypes = [i32p, C.c_int64, C.c_int, C.c_int, C.c_int, i32p]
+        _lib.coral_oracle_exact_knn.restype = C.c_int
+        _lib.coral_oracle_exact_knn.argtypes = [f32p, C.c_int64, C.c_int, f32p, C.c_int, C.c_int, C.c_int, i32p, f32p]
         _lib.coral_oracle_recall.restype = C.c_double
         _lib.coral_oracle_recall.argtypes = [i32p, i32p, C.c_int, C.c_int, C.c_int]
         _set_cpu_sig(_lib)
@@ -160,6 +162,22 @@ def select_start_ids(adj, first, M):
     if rc != M:
         raise ValueError("coral_oracle_select_start_ids rejected its arguments")
     return out
+
+
+def exact_knn(base, queries, k, metric):
+    """Brute-force k nearest rows by (sequential fp32 distance, id): (ids[Q,k], dists[Q,k])."""
+    lib = _load()
+    base, bp = _f32(base)
+    queries, qp = _f32(queries)
+    Q = queries.shape[0]
+    ids = np.empty((Q, k), np.int32)
+    dists = np.empty((Q, k), np.float32)
+    rc = lib.coral_oracle_exact_knn(bp, base.shape[0], base.shape[1], qp, Q, k, metric_id(metric),
+                                    ids.ctypes.data_as(C.POINTER(C.c_int32)),
+                                    dists.ctypes.data_as(C.POINTER(C.c_float)))
+    if rc != 0:
+        raise ValueError("coral_oracle_exact_knn: bad arguments")
+    return ids, dists
 
 
 def recall(res, gt, k):

@@ -7,6 +7,12 @@ whose every query fills its beam (the reference kernel reads out of range otherw
 whose distances do not tie exactly (the reference breaks ties by thread position), the
 reference kernel, the oracle and this library's kernel must return the same ids, the same
 distance bits and the same hop counts.
+
+The reference's hop count is not fully deterministic: in its replace-worst loop thread 0 clears
+``s_flag`` for the next pass before the other threads have tested it for the current one
+(src/search_gpu.cu:530-532), so a thread can leave the loop a pass early; on a B200 this shifts the
+hop total of a batch by one now and then (ids and distances were never seen to move).  The hop
+check therefore accepts the reference's value when any of three runs reproduces the oracle's.
 """
 import numpy as np
 import pytest
@@ -61,10 +67,14 @@ def test_reference_kernel_oracle_and_library_agree(name, make, Lk):
             r_ids, r_d, r_hops, _ = oracle.ref_gpu_search(c.base, c.adj, c.start, q, L, k, c.metric, c.max_degree)
             tag = f"{name} L={L} k={k}"
             _assert_rows_equal(tag + " reference kernel vs oracle", r_ids, r_d, o_ids, o_d)
-            assert r_hops == int(o_st[:, 4].sum()), f"{tag}: hops {r_hops} != oracle {int(o_st[:, 4].sum())}"
+            want_hops = int(o_st[:, 4].sum())
+            seen = [r_hops]
+            while seen[-1] != want_hops and len(seen) < 3:
+                seen.append(oracle.ref_gpu_search(c.base, c.adj, c.start, q, L, k, c.metric, c.max_degree)[2])
+            assert want_hops in seen, f"{tag}: reference hops {seen} never equal the oracle's {want_hops}"
             ids, d, st, hops = ix.search(q, L, k, dists=True, stats=True)
             _assert_rows_equal(tag + " library vs reference kernel", ids, d, r_ids, r_d)
-            assert hops == r_hops
+            assert hops == want_hops
 
 
 def test_per_query_hops_match_the_reference_kernel():
@@ -72,6 +82,9 @@ def test_per_query_hops_match_the_reference_kernel():
     L, k = 64, 10
     q, o_ids, o_d, o_st = _full_beam_queries(c, L, k)
     for i in range(8):
-        r_ids, r_d, r_hops, _ = oracle.ref_gpu_search(c.base, c.adj, c.start, q[i:i + 1], L, k, c.metric, c.max_degree)
-        assert r_hops == int(o_st[i, 4])
+        seen = []
+        while int(o_st[i, 4]) not in seen and len(seen) < 3:
+            r_ids, r_d, r_hops, _ = oracle.ref_gpu_search(c.base, c.adj, c.start, q[i:i + 1], L, k, c.metric, c.max_degree)
+            seen.append(r_hops)
+        assert int(o_st[i, 4]) in seen
         assert np.array_equal(r_d.view(np.uint32), o_d[i:i + 1].view(np.uint32))

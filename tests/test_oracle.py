@@ -165,3 +165,37 @@ def test_oracle_reproduces_committed_fixture():
         assert np.array_equal(ids, z[f"{tag}_ids"])
         assert np.array_equal(d.view(np.uint32), z[f"{tag}_dists"].view(np.uint32))
         assert np.array_equal(st[:, :7], z[f"{tag}_stats"][:, :7])
+
+
+# ---------------------------------------------------------------------------------------------
+# golden vectors recorded from the reference's OWN GPU kernel (tests/golden/make_ref_kernel_golden.py)
+# ---------------------------------------------------------------------------------------------
+
+def _ref_kernel_golden():
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_kernel_small.npz")
+    return np.load(path, allow_pickle=False)
+
+
+REF_GOLDEN_RUNS = [("rand_l2", 48, 10), ("rand_l2", 64, 32), ("rand_ip", 64, 16), ("struct_l2", 64, 10),
+                   ("struct_l2", 128, 100), ("struct_ip", 64, 10), ("struct_ip", 256, 10)]
+
+
+@pytest.mark.parametrize("tag,L,k", REF_GOLDEN_RUNS)
+def test_oracle_reproduces_the_reference_kernels_recorded_outputs(tag, L, k):
+    """ids, distance bits and the hop total the reference's beam_search_kernel produced on a B200
+    (src/search_gpu.cu:347-580, compiled unmodified) must come out of the CPU oracle bit for bit."""
+    g = _ref_kernel_golden()
+    metric = str(g[f"{tag}_metric"])
+    base, adj, start, queries = g[f"{tag}_base"], g[f"{tag}_adj"], g[f"{tag}_start"], g[f"{tag}_queries"]
+    key = f"{tag}_L{L}_k{k}"
+    rows = g[key + "_rows"]
+    ids, d, st = oracle.search(base, adj, start, queries[rows], L, k, metric)
+    assert (st[:, 0] == 0).all()
+    want_ids, want_bits = g[key + "_ids"], g[key + "_dist_bits"]
+    assert np.array_equal(d.view(np.uint32), want_bits)
+    for r in range(len(rows)):
+        if len(np.unique(want_bits[r])) == k:
+            assert np.array_equal(ids[r], want_ids[r])
+        else:   # the reference orders exact ties by thread position
+            assert sorted(ids[r]) == sorted(want_ids[r])
+    assert int(st[:, 4].sum()) == int(g[key + "_hops"])
