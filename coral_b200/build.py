@@ -16,8 +16,8 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libcoral_b200.so")
 LIB_CHECKED = os.path.join(LIB_DIR, "libcoral_b200_checked.so")
-SOURCES = ["search_kernel.cu", "plan.cu", "dense_topk.cu", "schedule.cu", "capi.cu", "search_static.cu", "start_select.cu"]
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+SOURCES = ["search_kernel.cu", "plan.cu", "dense_topk.cu", "build.cu", "schedule.cu", "capi.cu", "search_static.cu", "start_select.cu"]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--extended-lambda",
               "-Xcompiler", "-fPIC", "-shared"]
 
 

@@ -26,7 +26,8 @@ EXPORTS = (
     "coral_search_prepare", "coral_search_free", "coral_search", "coral_search_async",
     "coral_search_check", "coral_last_kernel_ms", "coral_last_total_ms", "coral_launch_count",
     "coral_set_option", "coral_get_option", "coral_count_hits", "coral_exact_knn", "coral_last_dense_ms",
-    "coral_last_dense_flops", "coral_merge_shards",
+    "coral_last_dense_flops", "coral_build_begin", "coral_build_nap", "coral_build_connect_enhance",
+    "coral_build_get_graph", "coral_build_set_graph", "coral_build_end", "coral_merge_shards",
     "coral_map_ids", "coral_last_error", "coral_search_static", "coral_search_static_status",
 )
 
@@ -78,6 +79,12 @@ def load():
         "coral_exact_knn": (C.c_int, [vp, f32p, C.c_int, C.c_int, i32p, f32p, i64p]),
         "coral_last_dense_ms": (C.c_float, [vp]),
         "coral_last_dense_flops": (C.c_double, [vp]),
+        "coral_build_begin": (C.c_int, [vp]),
+        "coral_build_nap": (C.c_int, [vp, i32p, C.c_int, C.c_int, C.c_int]),
+        "coral_build_connect_enhance": (C.c_int, [vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, i64p]),
+        "coral_build_get_graph": (C.c_int, [vp, i32p, f32p, i32p]),
+        "coral_build_set_graph": (C.c_int, [vp, i32p, f32p, i32p]),
+        "coral_build_end": (C.c_int, [vp]),
         "coral_merge_shards": (C.c_int, [vp, i32p, f32p, C.c_int, C.c_int, C.c_int, i32p, f32p, vp]),
         "coral_map_ids": (C.c_int, [vp, i32p, C.c_int64, i32p, vp]),
         "coral_last_error": (C.c_char_p, [vp]),
@@ -297,6 +304,39 @@ class Index:
     def last_dense_tflops(self) -> float:
         ms = float(self._lib.coral_last_dense_ms(self._h))
         return float(self._lib.coral_last_dense_flops(self._h)) / (ms * 1e-3) / 1e12 if ms > 0 else 0.0
+
+    # ---- graph build
+    def build_begin(self):
+        self._check(self._lib.coral_build_begin(self._h))
+
+    def build_nap(self, lists, batch: int = 0):
+        p, k = _ptr(lists, np.int32)
+        self._check(self._lib.coral_build_nap(self._h, p, int(k.shape[0]), int(k.shape[1]), int(batch)))
+
+    def build_connect_enhance(self, kb: int, L: int = 0, search_batch: int = 0, nap_batch: int = 0, M: int = 0) -> int:
+        n_iso = C.c_int64(0)
+        self._check(self._lib.coral_build_connect_enhance(self._h, int(kb), int(L), int(search_batch), int(nap_batch),
+                                                          int(M), C.byref(n_iso)))
+        return int(n_iso.value)
+
+    def build_get_graph(self):
+        """(adj[n, deg_pad] int32, dists[n, deg_pad] float32, deg[n] int32) as numpy arrays."""
+        deg_pad = self.get_option("deg_pad")
+        adj = np.empty((self.n, deg_pad), np.int32)
+        dd = np.empty((self.n, deg_pad), np.float32)
+        deg = np.empty(self.n, np.int32)
+        self._check(self._lib.coral_build_get_graph(self._h, C.c_void_p(adj.ctypes.data), C.c_void_p(dd.ctypes.data),
+                                                    C.c_void_p(deg.ctypes.data)))
+        return adj, dd, deg
+
+    def build_set_graph(self, adj, dists, deg):
+        a, ka = _ptr(adj, np.int32)
+        d, kd = _ptr(dists, np.float32)
+        g, kg = _ptr(deg, np.int32)
+        self._check(self._lib.coral_build_set_graph(self._h, a, d, g))
+
+    def build_end(self):
+        self._check(self._lib.coral_build_end(self._h))
 
     def merge_shards(self, d_ids, d_dists, stream=None):
         """d_ids/d_dists: CUDA tensors [G,Q,k] -> merged CUDA tensors ([Q,k], [Q,k])."""

@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "../../include/coral_b200.h"
+#include "build.cuh"
 #include "dense_topk.cuh"
 #include "plan.cuh"
 #include "schedule.cuh"
@@ -103,6 +104,14 @@ struct coral_index {
     unsigned long long* h_ctrl = nullptr;  // pinned mirror
     int64_t* d_hits = nullptr;
     std::map<int, std::pair<SearchPlan, int>> plans;  // L -> (plan, CTAs per SM)
+
+    // graph build (NAP + CE): distances of the stored edges, degrees, claim words, batch scratch
+    float* d_ndist = nullptr;
+    int32_t* d_deg = nullptr;
+    uint32_t* d_claim = nullptr;
+    void* d_nap_scratch = nullptr;
+    size_t nap_scratch_bytes = 0;
+    bool building = false;
 
     // dense tensor-core scans (exact k-NN): workspace kept between calls
     void* d_dense = nullptr;
@@ -394,6 +403,10 @@ int coral_index_destroy(coral_index_t* h) {
     cudaFree(h->d_ctrl);
     cudaFree(h->d_hits);
     cudaFree(h->d_dense);
+    cudaFree(h->d_ndist);
+    cudaFree(h->d_deg);
+    cudaFree(h->d_claim);
+    cudaFree(h->d_nap_scratch);
     if (h->h_ctrl) cudaFreeHost(h->h_ctrl);
     if (h->ev_t0) cudaEventDestroy(h->ev_t0);
     if (h->ev_k0) cudaEventDestroy(h->ev_k0);
@@ -953,6 +966,183 @@ int coral_exact_knn(coral_index_t* h, const float* queries, int Q, int k, int32_
 
 float coral_last_dense_ms(coral_index_t* h) { return h ? h->last_dense_ms : 0.f; }
 double coral_last_dense_flops(coral_index_t* h) { return h ? h->last_dense_flops : 0.0; }
+
+// ------------------------------------------------------------------ graph build
+
+static coral::BuildGraph build_view(coral_index* h) {
+    coral::BuildGraph g;
+    g.vecs = h->d_vecs;
+    g.adj = h->d_adj;
+    g.ndist = h->d_ndist;
+    g.deg = h->d_deg;
+    g.claim = h->d_claim;
+    g.n = h->n;
+    g.dim = h->dim;
+    g.deg_pad = h->deg_pad;
+    g.max_degree = h->max_degree;
+    g.metric = h->metric;
+    return g;
+}
+
+int coral_build_begin(coral_index_t* h) {
+    if (!h) return CORAL_ERR_ARG;
+    if (!h->d_vecs) return fail(h, CORAL_ERR_STATE, "build: set the vectors first");
+    if (int rc = ensure_device(h)) return rc;
+    const size_t cells = (size_t)h->n * h->deg_pad;
+    if (!h->d_adj) CK(cudaMalloc(&h->d_adj, cells * sizeof(int32_t)));
+    if (!h->d_ndist) CK(cudaMalloc(&h->d_ndist, cells * sizeof(float)));
+    if (!h->d_deg) CK(cudaMalloc(&h->d_deg, (size_t)h->n * sizeof(int32_t)));
+    if (!h->d_claim) CK(cudaMalloc(&h->d_claim, (size_t)h->n * sizeof(uint32_t)));
+    CK(cudaMemsetAsync(h->d_adj, 0xff, cells * sizeof(int32_t), h->stream));
+    CK(cudaMemsetAsync(h->d_ndist, 0, cells * sizeof(float), h->stream));
+    CK(cudaMemsetAsync(h->d_deg, 0, (size_t)h->n * sizeof(int32_t), h->stream));
+    CK(cudaMemsetAsync(h->d_claim, 0x7f, (size_t)h->n * sizeof(uint32_t), h->stream));
+    CK(cudaStreamSynchronize(h->stream));
+    h->building = true;
+    h->frontier_dirty = true;
+    return CORAL_OK;
+}
+
+int coral_build_set_graph(coral_index_t* h, const int32_t* adj, const float* dists, const int32_t* degs) {
+    if (!h || !adj || !dists || !degs) return fail(h, CORAL_ERR_ARG, "null argument");
+    if (!h->building) return fail(h, CORAL_ERR_STATE, "build: coral_build_begin has not been called");
+    if (int rc = ensure_device(h)) return rc;
+    const size_t cells = (size_t)h->n * h->deg_pad;
+    CK(cudaMemcpyAsync(h->d_adj, adj, cells * sizeof(int32_t), cudaMemcpyDefault, h->stream));
+    CK(cudaMemcpyAsync(h->d_ndist, dists, cells * sizeof(float), cudaMemcpyDefault, h->stream));
+    CK(cudaMemcpyAsync(h->d_deg, degs, (size_t)h->n * sizeof(int32_t), cudaMemcpyDefault, h->stream));
+    CK(cudaStreamSynchronize(h->stream));
+    h->frontier_dirty = true;
+    return CORAL_OK;
+}
+
+int coral_build_get_graph(coral_index_t* h, int32_t* adj_out, float* dists_out, int32_t* degs_out) {
+    if (!h) return CORAL_ERR_ARG;
+    if (!h->building) return fail(h, CORAL_ERR_STATE, "build: coral_build_begin has not been called");
+    if (int rc = ensure_device(h)) return rc;
+    const size_t cells = (size_t)h->n * h->deg_pad;
+    if (adj_out) CK(cudaMemcpyAsync(adj_out, h->d_adj, cells * sizeof(int32_t), cudaMemcpyDefault, h->stream));
+    if (dists_out) CK(cudaMemcpyAsync(dists_out, h->d_ndist, cells * sizeof(float), cudaMemcpyDefault, h->stream));
+    if (degs_out) CK(cudaMemcpyAsync(degs_out, h->d_deg, (size_t)h->n * sizeof(int32_t), cudaMemcpyDefault, h->stream));
+    CK(cudaStreamSynchronize(h->stream));
+    return CORAL_OK;
+}
+
+int coral_build_nap(coral_index_t* h, const int32_t* lists, int T, int kb, int batch) {
+    if (!h || (T > 0 && !lists) || T < 0) return fail(h, CORAL_ERR_ARG, "null argument");
+    if (!h->building) return fail(h, CORAL_ERR_STATE, "build: coral_build_begin has not been called");
+    if (kb < 2 || kb > 128 || kb + h->max_degree > 256) return fail(h, CORAL_ERR_LIMIT, "build: need 2 <= k_b <= 128 and k_b + max_degree <= 256");
+    if (batch <= 0) batch = 1024;                                    // config.json:5
+    if (int rc = ensure_device(h)) return rc;
+    if (T == 0) return CORAL_OK;
+    batch = std::min(batch, T);
+    const size_t need = coral::nap_scratch_bytes(batch, kb, h->max_degree) + (size_t)batch * kb * sizeof(int32_t);
+    if (need > h->nap_scratch_bytes) {
+        cudaFree(h->d_nap_scratch);
+        h->d_nap_scratch = nullptr;
+        h->nap_scratch_bytes = 0;
+        CK(cudaMalloc(&h->d_nap_scratch, need));
+        h->nap_scratch_bytes = need;
+    }
+    const bool dev = is_device_ptr(lists);
+    int32_t* d_stage = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(h->d_nap_scratch) +
+                                                  coral::nap_scratch_bytes(batch, kb, h->max_degree));
+    const coral::BuildGraph g = build_view(h);
+    for (int s = 0; s < T; s += batch) {                              // src/index_gpu.cpp:555-560: batch after batch
+        const int B = std::min(batch, T - s);
+        const int32_t* src = lists + (size_t)s * kb;
+        if (!dev) {
+            CK(cudaMemcpyAsync(d_stage, src, (size_t)B * kb * sizeof(int32_t), cudaMemcpyHostToDevice, h->stream));
+            src = d_stage;
+        }
+        CK(coral::nap_batch(g, src, B, kb, h->d_nap_scratch, h->stream, &h->launches));
+        if (!dev) CK(cudaStreamSynchronize(h->stream));              // the staging buffer is reused
+    }
+    CK(cudaStreamSynchronize(h->stream));
+    h->frontier_dirty = true;
+    return CORAL_OK;
+}
+
+int coral_build_connect_enhance(coral_index_t* h, int kb, int L, int search_batch, int nap_batch, int M,
+                                int64_t* n_isolated_out) {
+    if (!h) return CORAL_ERR_ARG;
+    if (!h->building) return fail(h, CORAL_ERR_STATE, "build: coral_build_begin has not been called");
+    if (kb < 1 || kb > 128) return fail(h, CORAL_ERR_LIMIT, "build: need 1 <= k_b <= 128");
+    if (L <= 0) L = 256;                                              // src/enhance.cu:783
+    if (search_batch <= 0) search_batch = 524288;                     // config.json:7
+    if (nap_batch <= 0) nap_batch = 4096;                             // config.json:6
+    if (M <= 0) M = 16;                                               // config.json:29
+    if (kb > L || M > L) return fail(h, CORAL_ERR_ARG, "build: need k_b <= L and M <= L");
+    if (int rc = ensure_device(h)) return rc;
+    std::vector<int32_t> degs((size_t)h->n);
+    CK(cudaMemcpy(degs.data(), h->d_deg, degs.size() * sizeof(int32_t), cudaMemcpyDeviceToHost));
+    std::vector<int32_t> iso;                                         // src/enhance.cu:582-607, ascending ids
+    int first_connected = -1;
+    for (int64_t i = 0; i < h->n; ++i) {
+        if (degs[(size_t)i] == 0) iso.push_back((int32_t)i);
+        else if (first_connected < 0) first_connected = (int)i;
+    }
+    std::vector<int32_t>().swap(degs);
+    if (n_isolated_out) *n_isolated_out = (int64_t)iso.size();
+    if (iso.empty()) return CORAL_OK;
+    if (first_connected < 0) return fail(h, CORAL_ERR_STATE, "build: no node has an out-edge yet");
+    const int qmax = (int)std::min<size_t>((size_t)search_batch, iso.size());
+    if (int rc = coral_search_prepare(h, qmax, L, kb)) return rc;
+    int32_t *d_iso = nullptr, *d_res_ids = nullptr;
+    float *d_res_d = nullptr, *d_q = nullptr;
+    cudaError_t e = cudaMalloc(&d_iso, iso.size() * sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&d_res_ids, (size_t)qmax * kb * sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&d_res_d, (size_t)qmax * kb * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&d_q, (size_t)qmax * h->dim * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemcpy(d_iso, iso.data(), iso.size() * sizeof(int32_t), cudaMemcpyHostToDevice);
+    int rc = CORAL_OK;
+    const coral::BuildGraph g = build_view(h);
+    for (size_t s = 0; s < iso.size() && e == cudaSuccess && rc == CORAL_OK; s += (size_t)search_batch) {
+        const int nq = (int)std::min<size_t>((size_t)search_batch, iso.size() - s);
+        // entry points of this search batch (src/enhance.cu:793): farthest-point sampling from the
+        // lowest-numbered node with an out-edge
+        rc = coral_index_select_start_ids(h, first_connected, M, nullptr);
+        if (rc != CORAL_OK) break;
+        e = coral::gather_rows(h->d_vecs, d_iso + s, nq, h->dim, d_q, h->stream);
+        h->launches += 1;
+        if (e != cudaSuccess) break;
+        rc = enqueue_search(h, d_q, nq, L, kb, d_res_ids, d_res_d, nullptr, h->stream);   // src/enhance.cu:794
+        if (rc != CORAL_OK) break;
+        e = cudaStreamSynchronize(h->stream);
+        if (e != cudaSuccess) break;
+        rc = coral_search_check(h);
+        if (rc != CORAL_OK) break;
+        for (int j = 0; j < nq && e == cudaSuccess; j += nap_batch) {                       // src/enhance.cu:795-800
+            const int nb = std::min(nap_batch, nq - j);
+            e = coral::ce_batch(g, d_iso + s + j, nb, d_res_ids + (size_t)j * kb, d_res_d + (size_t)j * kb, kb, h->stream,
+                                &h->launches);
+        }
+        if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+        h->frontier_dirty = true;
+    }
+    cudaFree(d_iso);
+    cudaFree(d_res_ids);
+    cudaFree(d_res_d);
+    cudaFree(d_q);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(h, CORAL_ERR_CUDA, std::string("build: ") + cudaGetErrorString(e));
+    }
+    return rc;
+}
+
+int coral_build_end(coral_index_t* h) {
+    if (!h) return CORAL_ERR_ARG;
+    if (int rc = ensure_device(h)) return rc;
+    cudaStreamSynchronize(h->stream);
+    cudaFree(h->d_ndist);        h->d_ndist = nullptr;
+    cudaFree(h->d_deg);          h->d_deg = nullptr;
+    cudaFree(h->d_claim);        h->d_claim = nullptr;
+    cudaFree(h->d_nap_scratch);  h->d_nap_scratch = nullptr;
+    h->nap_scratch_bytes = 0;
+    h->building = false;
+    return CORAL_OK;
+}
 
 int coral_merge_shards(coral_index_t* h, const int32_t* d_ids, const float* d_dists, int G, int Q, int k,
                        int32_t* d_ids_out, float* d_dists_out, void* stream) {

@@ -205,6 +205,49 @@ int coral_exact_knn(coral_index_t* h, const float* queries, int Q, int k, int32_
 float coral_last_dense_ms(coral_index_t* h);
 double coral_last_dense_flops(coral_index_t* h);
 
+/* ---- graph build (the callers of the search path on the build side) ----
+ *
+ * Replaces the HBM-tier build of IndexGPU::BuildGPU (src/index_gpu.cpp:308-383): the exact
+ * nearest-neighbour lists of the training queries (coral_exact_knn) are projected onto the base
+ * set batch by batch (coral_build_nap), then nodes no list reached are connected by searching
+ * the partial graph with their own vector (coral_build_connect_enhance).  The graph lives in
+ * the handle's adjacency, so it can be searched at any point; rows are kept closest-first with
+ * the distance of every edge, like the reference's Slot (include/disk_graph.h:30-35).  Where
+ * the reference lets thread arrival order decide (src/upd_gpu.cu:102, src/enhance.cu:166) the
+ * lowest index wins, so a build is reproducible. */
+
+/* Replaces Graph::Graph in Mode::CONS (include/graph.cuh:222-266): an empty graph over the
+ * handle's vectors (every degree 0); allocates the edge distances and build scratch. */
+int coral_build_begin(coral_index_t* h);
+
+/* Replaces GPUFuncs::graph_update / gpu_neibor_aware (src/upd_disk.cu:218, src/upd_gpu.cu:260-303)
+ * for T lists of kb base ids (host or device, row-major), `batch` lists at a time (0 = 1024,
+ * config.json:5): per list member, candidates = the other members (skipping pairs of already
+ * connected nodes) + its current neighbours, sorted by distance, occlusion-pruned, kept ones
+ * first then pruned ones up to max_degree.  2 <= kb <= 128, kb + max_degree <= 256. */
+int coral_build_nap(coral_index_t* h, const int32_t* lists, int T, int kb, int batch);
+
+/* Replaces GPUFuncs::gpu_connect_enhance, enhance_mode 0 (src/enhance.cu:728-812): every node
+ * of degree 0, in batches of `search_batch` (0 = 524288), is searched with its own vector
+ * (beam capacity L, 0 = 256; kb results) from M (0 = 16) entry points chosen per batch by
+ * coral_index_select_start_ids from the lowest-numbered connected node; then, `nap_batch`
+ * (0 = 4096) nodes at a time, the found nodes receive a reverse edge (src/enhance.cu:136-212)
+ * and the node gets its own pruned row.  Calls coral_search_prepare (sizes: search_batch, L,
+ * kb) and leaves the last batch's entry points installed, as the reference's save_build does.
+ * The reference's second phase ("top hit" nodes, src/enhance.cu:814-856) is not built. */
+int coral_build_connect_enhance(coral_index_t* h, int kb, int L, int search_batch, int nap_batch, int M,
+                                int64_t* n_isolated_out);
+
+/* Reads / replaces the graph under construction: adjacency [n][deg_pad] (-1 padding), edge
+ * distances [n][deg_pad], degrees [n]; host or device pointers, NULL = skip (get only).
+ * Replaces Graph::save_build / load (include/graph.cuh:481-484) at the C boundary. */
+int coral_build_get_graph(coral_index_t* h, int32_t* adj_out, float* dists_out, int32_t* degs_out);
+int coral_build_set_graph(coral_index_t* h, const int32_t* adj, const float* dists, const int32_t* degs);
+
+/* Replaces GPUFuncs::Build_Free: releases the edge distances and build scratch; the adjacency
+ * (and the installed entry points) stay for searching. */
+int coral_build_end(coral_index_t* h);
+
 /* Shard merge (no counterpart in the reference, which is single-GPU): ids and
  * dists hold G per-shard results [G][Q][k] (global ids, -1 = padding); writes
  * the k closest per query by (distance, id).  Device pointers; enqueued on

@@ -11,6 +11,7 @@
  * Here the distance is the reference's own device function (include/utils.cuh:254-275, :307-323:
  * one sequential fp32 fused chain) and ties order by the smaller id.
  */
+#define _GNU_SOURCE
 #include <math.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -59,6 +60,251 @@ int coral_oracle_exact_knn(const float* base, int64_t n, int dim, const float* q
             }
         }
         free(keys);
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------------------------------------
+ * Graph build: neighbourhood-aware projection (NAP) and connectivity enhancement (CE).
+ *
+ *   NAP   GPUFuncs::gpu_neibor_aware          src/upd_gpu.cu:260-303
+ *           pair_dist_compute_kernel          src/upd_gpu.cu:12-78     candidates of every list member
+ *           segmented sort by distance        src/utils.cu:340-346     (IP: descending)
+ *           candidate_ignore_kernel           src/upd_gpu.cu:203-247   occlusion pruning
+ *           update_new_nbrs_kernel            src/upd_gpu.cu:88-167    need_discard = 1 (config.json:15)
+ *   CE    GPUFuncs::gpu_connect_enhance       src/enhance.cu:728-861   enhance_mode 0, isolated nodes
+ *           build_candidate_kernel            src/enhance.cu:136-212   candidates + reverse edges
+ *           candidate_ignore_kernel_for_iso   src/enhance.cu:344-389
+ *           update_iso_nbrs_kernel            src/enhance.cu:528-580
+ *
+ * The graph is held as in the CUDA library: adj[n][deg_pad] (-1 padding), ndist[n][deg_pad] (the
+ * reference's Slot::dists), deg[n].  Rows are kept closest-first, as the reference keeps them.
+ *
+ * Where the reference lets thread arrival order decide, this restatement (and the CUDA path) fix
+ * the lowest index:
+ *   - a node that is a member of several lists of one batch is updated by its FIRST occurrence in
+ *     the batch (reference: whichever thread wins atomicTestAndSetBit, src/upd_gpu.cu:102);
+ *   - a node found by several isolated nodes of one CE batch receives the reverse edge of the first
+ *     (isolated node, result rank) pair (reference: src/enhance.cu:166);
+ *   - the segmented sorts are stable (equal distances keep their candidate order).
+ * Every other step is deterministic in the reference and restated literally.
+ * ------------------------------------------------------------------------------------------------ */
+
+enum { S_INVALID = 0, S_INITIAL = 1, S_DISCARDED = 2, S_RETAINED = 3, S_REPEATED = 4 };  /* include/uni.h:140-146 */
+
+typedef struct {
+    int id;
+    int col;      /* position in the unsorted candidate row (stable sort key) */
+    int status;
+    float dist;
+} Cand;
+
+static inline float farthest_of(int metric) { return metric == ORACLE_L2 ? 3.402823466e+38f : -3.402823466e+38f; }
+/* include/utils.cuh:380-382: true when d1 is closer than d0 */
+static inline int closer(float d0, float d1, int metric) { return metric == ORACLE_L2 ? d0 > d1 : d0 < d1; }
+
+static int cmp_cand(const void* a, const void* b, void* metric_p) {
+    const Cand* x = (const Cand*)a;
+    const Cand* y = (const Cand*)b;
+    const int metric = *(const int*)metric_p;
+    const uint32_t ox = ord_of(x->dist, metric), oy = ord_of(y->dist, metric);
+    if (ox != oy) return ox < oy ? -1 : 1;
+    return x->col < y->col ? -1 : (x->col > y->col ? 1 : 0);
+}
+
+/* src/upd_gpu.cu:203-247 (and src/enhance.cu:344-389, the same rule run by a block). */
+static void occlusion_prune(const float* base, int dim, int metric, Cand* c, int n_cand, int max_degree) {
+    int nbr_num = 0;
+    for (int i = 0; i < n_cand && nbr_num < max_degree; ++i) {
+        if (c[i].status == S_INVALID) break;
+        if (c[i].status == S_INITIAL) {
+            c[i].status = S_RETAINED;
+            ++nbr_num;
+            const float* vi = base + (size_t)c[i].id * dim;
+            for (int j = i + 1; j < n_cand; ++j) {
+                if (c[j].status == S_INVALID) break;
+                if (c[j].id == c[i].id)
+                    c[j].status = S_REPEATED;
+                else if (c[j].status == S_INITIAL) {
+                    const float dij = coral_oracle_dist_seq(vi, base + (size_t)c[j].id * dim, dim, metric);
+                    if (closer(c[j].dist, dij, metric)) c[j].status = S_DISCARDED;
+                }
+            }
+        } else if (c[i].status == S_DISCARDED) {
+            for (int j = i + 1; j < n_cand; ++j) {
+                if (c[j].id == c[i].id)
+                    c[j].status = S_REPEATED;
+                else if (c[j].status == S_INVALID)
+                    break;
+            }
+        }
+    }
+}
+
+/* src/upd_gpu.cu:106-135 / src/enhance.cu:544-570: kept first, then pruned ones to fill the row. */
+static int fill_row(const Cand* c, int n_cand, int max_degree, int32_t* nbrs, float* dists) {
+    int retained = 0;
+    for (int i = 0; i < n_cand; ++i) {
+        if (c[i].status == S_RETAINED) ++retained;
+        else if (c[i].status == S_INVALID) break;
+    }
+    int discarded_need = max_degree - retained, nbr_num = 0;
+    for (int j = 0; j < n_cand && nbr_num < max_degree; ++j) {
+        if (c[j].status == S_RETAINED) {
+            nbrs[nbr_num] = c[j].id;
+            dists[nbr_num++] = c[j].dist;
+        } else if (c[j].status == S_DISCARDED && (discarded_need--) > 0) {
+            nbrs[nbr_num] = c[j].id;
+            dists[nbr_num++] = c[j].dist;
+        } else if (c[j].status == S_INVALID)
+            break;
+    }
+    return nbr_num;
+}
+
+/* One NAP batch: B lists of kb base ids; every pivot sees the graph as it was before the batch. */
+int coral_oracle_nap_batch(const float* base, int64_t n, int dim, int metric, int max_degree, int deg_pad,
+                           int32_t* adj, float* ndist, int32_t* deg, const int32_t* lists, int B, int kb) {
+    if (!base || !adj || !ndist || !deg || !lists || B < 0 || kb < 2 || max_degree > deg_pad) return -1;
+    const int cand_size = kb + max_degree;
+    const int64_t pivots = (int64_t)B * kb;
+    /* first occurrence of every node in the batch */
+    int64_t* first = (int64_t*)malloc((size_t)n * sizeof(int64_t));
+    for (int64_t i = 0; i < n; ++i) first[i] = -1;
+    for (int64_t p = 0; p < pivots; ++p) {
+        const int id = lists[p];
+        if (id < 0 || id >= n) { free(first); return -2; }
+        if (first[id] < 0) first[id] = p;
+    }
+    int32_t* new_nbrs = (int32_t*)malloc((size_t)pivots * max_degree * sizeof(int32_t));
+    float* new_dists = (float*)malloc((size_t)pivots * max_degree * sizeof(float));
+    int32_t* new_deg = (int32_t*)malloc((size_t)pivots * sizeof(int32_t));
+#pragma omp parallel
+    {
+        Cand* c = (Cand*)malloc((size_t)cand_size * sizeof(Cand));
+#pragma omp for schedule(dynamic, 16)
+        for (int64_t p = 0; p < pivots; ++p) {
+            new_deg[p] = -1;
+            const int row_id = lists[p];
+            if (first[row_id] != p) continue;                       /* src/upd_gpu.cu:102 */
+            const int32_t* ids = lists + (p / kb) * kb;
+            const int i = (int)(p % kb);
+            const int row_deg = deg[row_id];
+            for (int col = 0; col < cand_size; ++col) {             /* src/upd_gpu.cu:36-73 */
+                Cand* e = &c[col];
+                e->col = col;
+                e->id = -1;
+                e->status = S_INVALID;
+                e->dist = farthest_of(metric);
+                if (col >= kb + row_deg || col == i) continue;
+                if (col >= kb) {
+                    e->id = adj[(size_t)row_id * deg_pad + (col - kb)];
+                    e->dist = ndist[(size_t)row_id * deg_pad + (col - kb)];
+                    e->status = S_INITIAL;
+                } else {
+                    const int col_id = ids[col];
+                    if (col_id == row_id) continue;
+                    if (row_deg > 0 && deg[col_id] > 0) continue;
+                    e->id = col_id;
+                    e->dist = coral_oracle_dist_seq(base + (size_t)row_id * dim, base + (size_t)col_id * dim, dim, metric);
+                    e->status = S_INITIAL;
+                }
+            }
+            qsort_r(c, (size_t)cand_size, sizeof(Cand), cmp_cand, &metric);
+            occlusion_prune(base, dim, metric, c, cand_size, max_degree);
+            new_deg[p] = fill_row(c, cand_size, max_degree, new_nbrs + (size_t)p * max_degree, new_dists + (size_t)p * max_degree);
+        }
+        free(c);
+    }
+    for (int64_t p = 0; p < pivots; ++p) {
+        if (new_deg[p] < 0) continue;
+        const int id = lists[p];
+        for (int j = 0; j < deg_pad; ++j) {
+            adj[(size_t)id * deg_pad + j] = j < new_deg[p] ? new_nbrs[(size_t)p * max_degree + j] : -1;
+            ndist[(size_t)id * deg_pad + j] = j < new_deg[p] ? new_dists[(size_t)p * max_degree + j] : 0.f;
+        }
+        deg[id] = new_deg[p];
+    }
+    free(first); free(new_nbrs); free(new_dists); free(new_deg);
+    return 0;
+}
+
+/* One CE batch (src/enhance.cu:640-668): n_iso isolated nodes with their kb search results
+ * (res_ids < 0 = padding).  Reverse edges first (src/enhance.cu:136-212), then every isolated node's
+ * own row from its pruned results. */
+int coral_oracle_ce_batch(const float* base, int64_t n, int dim, int metric, int max_degree, int deg_pad,
+                          int32_t* adj, float* ndist, int32_t* deg, const int32_t* iso_ids, int n_iso,
+                          const int32_t* res_ids, const float* res_dists, int kb) {
+    if (!base || !adj || !ndist || !deg || !iso_ids || !res_ids || !res_dists || n_iso < 0 || kb < 1) return -1;
+    /* first (isolated node, rank) pair that names each found node */
+    int64_t* first = (int64_t*)malloc((size_t)n * sizeof(int64_t));
+    for (int64_t i = 0; i < n; ++i) first[i] = -1;
+    for (int64_t e = 0; e < (int64_t)n_iso * kb; ++e) {
+        const int id = res_ids[e];
+        if (id >= 0 && id < n && first[id] < 0) first[id] = e;
+    }
+#pragma omp parallel for schedule(dynamic, 64)
+    for (int64_t e = 0; e < (int64_t)n_iso * kb; ++e) {
+        const int knn_id = res_ids[e];
+        if (knn_id < 0 || knn_id >= n || first[knn_id] != e) continue;
+        const int iso_id = iso_ids[e / kb];
+        const float knn_dist = res_dists[e];
+        const float* iso_vec = base + (size_t)iso_id * dim;
+        int32_t* nb = adj + (size_t)knn_id * deg_pad;
+        float* ds = ndist + (size_t)knn_id * deg_pad;
+        const int d = deg[knn_id];
+        int pos = 0, valid = 1, out_pos;
+        for (; pos < d; ++pos) {
+            if (closer(knn_dist, ds[pos], metric)) {
+                if (valid && closer(knn_dist, coral_oracle_dist_seq(iso_vec, base + (size_t)nb[pos] * dim, dim, metric), metric))
+                    valid = 0;
+            } else
+                break;
+        }
+        if (d == max_degree) {
+            if (!valid || pos >= d) continue;
+            out_pos = d - 1;
+            for (; out_pos >= pos; --out_pos)
+                if (closer(ds[out_pos], coral_oracle_dist_seq(iso_vec, base + (size_t)nb[out_pos] * dim, dim, metric), metric))
+                    break;
+            if (out_pos < pos) out_pos = d - 1;
+        } else {
+            out_pos = d;
+            deg[knn_id] = d + 1;
+        }
+        for (int j = out_pos; j > pos; --j) {
+            nb[j] = nb[j - 1];
+            ds[j] = ds[j - 1];
+        }
+        nb[pos] = iso_id;
+        ds[pos] = knn_dist;
+    }
+    free(first);
+#pragma omp parallel
+    {
+        Cand* c = (Cand*)malloc((size_t)kb * sizeof(Cand));
+        int32_t* row_n = (int32_t*)malloc((size_t)max_degree * sizeof(int32_t));
+        float* row_d = (float*)malloc((size_t)max_degree * sizeof(float));
+#pragma omp for schedule(dynamic, 16)
+        for (int i = 0; i < n_iso; ++i) {
+            for (int r = 0; r < kb; ++r) {
+                const int id = res_ids[(size_t)i * kb + r];
+                c[r].col = r;
+                c[r].id = id >= 0 && id < n ? id : -1;
+                c[r].status = c[r].id >= 0 ? S_INITIAL : S_INVALID;
+                c[r].dist = c[r].id >= 0 ? res_dists[(size_t)i * kb + r] : farthest_of(metric);
+            }
+            qsort_r(c, (size_t)kb, sizeof(Cand), cmp_cand, &metric);
+            occlusion_prune(base, dim, metric, c, kb, max_degree);
+            const int nd = fill_row(c, kb, max_degree, row_n, row_d);
+            const int id = iso_ids[i];
+            for (int j = 0; j < deg_pad; ++j) {
+                adj[(size_t)id * deg_pad + j] = j < nd ? row_n[j] : -1;
+                ndist[(size_t)id * deg_pad + j] = j < nd ? row_d[j] : 0.f;
+            }
+            deg[id] = nd;
+        }
+        free(c); free(row_n); free(row_d);
     }
     return 0;
 }

@@ -64,6 +64,12 @@ def _load():
         _lib.coral_oracle_select_start_ids.argtypes = [i32p, C.c_int64, C.c_int, C.c_int, C.c_int, i32p]
         _lib.coral_oracle_exact_knn.restype = C.c_int
         _lib.coral_oracle_exact_knn.argtypes = [f32p, C.c_int64, C.c_int, f32p, C.c_int, C.c_int, C.c_int, i32p, f32p]
+        _lib.coral_oracle_nap_batch.restype = C.c_int
+        _lib.coral_oracle_nap_batch.argtypes = [f32p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, i32p, f32p, i32p,
+                                                i32p, C.c_int, C.c_int]
+        _lib.coral_oracle_ce_batch.restype = C.c_int
+        _lib.coral_oracle_ce_batch.argtypes = [f32p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, i32p, f32p, i32p,
+                                               i32p, C.c_int, i32p, f32p, C.c_int]
         _lib.coral_oracle_recall.restype = C.c_double
         _lib.coral_oracle_recall.argtypes = [i32p, i32p, C.c_int, C.c_int, C.c_int]
         _set_cpu_sig(_lib)
@@ -178,6 +184,74 @@ def exact_knn(base, queries, k, metric):
     if rc != 0:
         raise ValueError("coral_oracle_exact_knn: bad arguments")
     return ids, dists
+
+
+class BuildState:
+    """Graph under construction as the CUDA library holds it: adj / ndist [n, deg_pad], deg [n]."""
+
+    def __init__(self, n, max_degree):
+        self.max_degree = int(max_degree)
+        self.deg_pad = 32 if max_degree <= 32 else (64 if max_degree <= 64 else 128)
+        self.adj = np.full((n, self.deg_pad), -1, np.int32)
+        self.ndist = np.zeros((n, self.deg_pad), np.float32)
+        self.deg = np.zeros(n, np.int32)
+
+
+def nap_batch(base, state, lists, metric):
+    """One batch of the neighbourhood-aware projection (src/upd_gpu.cu:260-303) in place."""
+    lib = _load()
+    base, bp = _f32(base)
+    lists, lp = _i32(lists)
+    i32p, f32p = C.POINTER(C.c_int32), C.POINTER(C.c_float)
+    rc = lib.coral_oracle_nap_batch(bp, base.shape[0], base.shape[1], metric_id(metric), state.max_degree,
+                                    state.deg_pad, state.adj.ctypes.data_as(i32p), state.ndist.ctypes.data_as(f32p),
+                                    state.deg.ctypes.data_as(i32p), lp, lists.shape[0], lists.shape[1])
+    if rc != 0:
+        raise ValueError(f"coral_oracle_nap_batch failed with {rc}")
+
+
+def ce_batch(base, state, iso_ids, res_ids, res_dists, metric):
+    """One batch of the connectivity enhancement (src/enhance.cu:640-668) in place."""
+    lib = _load()
+    base, bp = _f32(base)
+    iso_ids, ip_ = _i32(iso_ids)
+    res_ids, rp = _i32(res_ids)
+    res_dists, dp = _f32(res_dists)
+    i32p, f32p = C.POINTER(C.c_int32), C.POINTER(C.c_float)
+    rc = lib.coral_oracle_ce_batch(bp, base.shape[0], base.shape[1], metric_id(metric), state.max_degree,
+                                   state.deg_pad, state.adj.ctypes.data_as(i32p), state.ndist.ctypes.data_as(f32p),
+                                   state.deg.ctypes.data_as(i32p), ip_, len(iso_ids), rp, dp, res_ids.shape[1])
+    if rc != 0:
+        raise ValueError(f"coral_oracle_ce_batch failed with {rc}")
+
+
+def build_graph(base, train_knn, metric, max_degree, batch=1024, ce=True, ce_L=256, ce_search_batch=524288,
+                ce_nap_batch=4096, n_start=16, log=None):
+    """The reference's build on the CPU: NAP over the training lists in batches (src/index_gpu.cpp:501-580,
+    config.json:5), then CE of the isolated nodes (src/enhance.cu:728-812): per search batch entry
+    points by farthest-point sampling from the lowest-numbered node with an out-edge, the full
+    expansion search with L = 256 and k = k_b, then batches of reverse edges and pruned rows.
+    Returns (BuildState, start_ids)."""
+    base = np.ascontiguousarray(base, np.float32)
+    train_knn = np.ascontiguousarray(train_knn, np.int32)
+    st = BuildState(base.shape[0], max_degree)
+    for s in range(0, train_knn.shape[0], batch):
+        nap_batch(base, st, train_knn[s:s + batch], metric)
+    start = None
+    if ce:
+        kb = train_knn.shape[1]
+        iso = np.nonzero(st.deg == 0)[0].astype(np.int32)
+        if log:
+            log(f"oracle build: {len(iso)} isolated nodes after NAP")
+        for s in range(0, len(iso), ce_search_batch):
+            chunk = iso[s:s + ce_search_batch]
+            start = select_start_ids(st.adj, int(np.nonzero(st.deg > 0)[0][0]), n_start)
+            ids, dists, _ = search(base, st.adj, start, base[chunk], ce_L, kb, metric)
+            for j in range(0, len(chunk), ce_nap_batch):
+                ce_batch(base, st, chunk[j:j + ce_nap_batch], ids[j:j + ce_nap_batch], dists[j:j + ce_nap_batch], metric)
+    if start is None:
+        start = select_start_ids(st.adj, int(np.nonzero(st.deg > 0)[0][0]), n_start)
+    return st, start
 
 
 def recall(res, gt, k):

@@ -24,7 +24,7 @@ SPECS = (
     # tag, case factory, (L, k) pairs, store the inputs in the fixture?
     ("rand_l2", lambda: cases.random_case("l2", 1000, 40, 32, 24, m=16, seed=77), [(48, 10), (64, 32)], True),
     ("rand_ip", lambda: cases.random_case("ip", 1000, 64, 64, 24, m=16, seed=77, dup_start=True), [(64, 16)], True),
-    ("struct_l2", lambda: cases.structured("l2", n=3000, dim=32, deg=32, nq=48), [(64, 10), (128, 100)], True),
+    ("struct_l2", lambda: cases.structured("l2", n=3000, dim=64, deg=32, nq=48), [(64, 10), (128, 100)], True),
     ("struct_ip", lambda: cases.structured("ip", n=3000, dim=48, deg=64, nq=48), [(64, 10), (256, 10)], True),
 )
 
