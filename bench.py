@@ -1,23 +1,28 @@
 #!/usr/bin/env python
 """Benchmark of the batched graph beam search (one JSON line on rank 0).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3|c2|c1|c4|small]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3|c2|c1|c4|c5|small]
     python bench.py --impl reference ...      # the reference's CPU best-first search, host cores
 
-A step is one pass of the search over the workload's whole query batch.
+A step is one pass of the search over the workload's whole query batch.  The index is built in
+this process by the library itself, the way the reference builds it: exact k_b nearest base points
+of the training queries (tensor cores), neighbourhood-aware projection, connectivity enhancement,
+16 entry points by farthest-point sampling.
 
-Replicated workloads (c1, c2, c3, small): with N GPUs every rank holds the whole index and
-searches a contiguous 1/N slice of the batch -- no collective on the data path, total work
-fixed (strong scaling).  Sharded workload (c4): every rank holds one 12.5M-point shard with
-its own graph, searches ALL queries, and the per-shard top-k are exchanged with one NCCL
-all-gather and merged (weak scaling: the index grows with N).
+Replicated workloads (c1, c2, c3, small): with N GPUs every rank holds the whole index and searches
+1/N of the batch -- the N-th part of the batch in its locality ORDER (every rank computes the same
+deterministic order of the whole batch), no collective on the data path, total work fixed (strong
+scaling).  With N > 1 the run ends with a short sharded leg (one 1M-point shard per GPU, all queries
+on every shard, one NCCL all-gather, slice merge), checked against the CPU oracle's merge and
+reported under config.sharded_check.  Sharded workload (c4): every rank holds one 12.5M-point shard
+with its own graph and searches ALL queries (weak scaling: the index grows with N).
 
 value : queries/s with index and queries resident in HBM, device pointers in and out
         (coral_search_async), CUDA events on the launching stream, max over ranks.
 e2e   : queries/s through coral_search with pinned HOST queries in and HOST ids out, the
         copies inside the timed region.
-Inputs are seeded synthetic data of the named shapes (coral_b200/synth.py); the index
-(vectors + adjacency) is far larger than L2, so no cache flush is needed between iterations.
+Inputs are seeded synthetic data of the named shapes (coral_b200/synth.py); the index (vectors +
+adjacency) is far larger than L2, so no cache flush is needed between iterations.
 """
 from __future__ import annotations
 
@@ -35,25 +40,20 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # n: base points (per shard when sharded), groups: mixture centres / clusters
-    "c1": dict(n=1_000_000, dim=200, metric="l2", deg=32, groups=1000, q=10_000, k=10, Ls=[64, 128, 256, 512], train=100_000),
-    "c2": dict(n=1_000_000, dim=512, metric="ip", deg=32, groups=410, q=10_000, k=10, Ls=[64, 128, 256], train=100_000),
-    "c3": dict(n=10_000_000, dim=512, metric="ip", deg=64, groups=4096, q=100_000, k=10, Ls=[64, 128, 256], train=100_000),
-    "c4": dict(n=12_500_000, dim=200, metric="l2", deg=32, groups=10_000, q=100_000, k=100, Ls=[128, 256], train=100_000,
-               sharded=True),
-    "small": dict(n=1_000_000, dim=512, metric="ip", deg=64, groups=410, q=8_192, k=10, Ls=[64], train=50_000),
+    # data: a configuration of coral_b200.synth.CONFIGS; n: base points (per shard when sharded)
+    "c1": dict(data="c1", n=1_000_000, q=10_000, k=10, Ls=[64, 128, 256, 512], train=100_000),
+    "c2": dict(data="c2", n=1_000_000, q=10_000, k=10, Ls=[64, 128, 256], train=100_000),
+    "c3": dict(data="c3", n=10_000_000, q=100_000, k=10, Ls=[64, 128, 256], train=100_000),
+    "c4": dict(data="c4", n=12_500_000, q=100_000, k=100, Ls=[128, 256], train=100_000, sharded=True),
+    "small": dict(data="c3", n=1_000_000, q=8_192, k=10, Ls=[64], train=100_000),
     # small-batch latency on the c3 index: batches of 1, 8, 64, 512 queries, L=128
-    "c5": dict(n=10_000_000, dim=512, metric="ip", deg=64, groups=4096, q=8_192, k=10, Ls=[128], train=100_000,
-               latency=[1, 8, 64, 512]),
+    "c5": dict(data="c3", n=10_000_000, q=8_192, k=10, Ls=[128], train=100_000, latency=[1, 8, 64, 512]),
 }
 METRIC = "QPS @ recall@10>=0.95, 10Mx512 IP"
 PEAK_FALLBACK_GBS = 6650.0
-# DRAM bytes moved by one full-size launch, from the single-pass ncu capture recorded in
-# profiles/ (workload, L) -> bytes; absent -> null in the JSON line.
-MEASURED_TRAFFIC = {
-    ("c3", 64): 3.916e11,      # dram__bytes_read 366.0 GB + dram__bytes_write 25.6 GB for 100k queries (locality-ordered)
-    ("small", 64): 1.201e10,   # 10.64 GB + 1.37 GB for 8192 queries
-}
+# DRAM bytes per algorithmic byte of the search kernel, from the ncu captures summarised under
+# profiles/ (a profile constant, not a measurement of this run): workload -> ratio.
+DRAM_PER_ALGORITHMIC_BYTE = {}
 
 
 def log(*a):
@@ -110,92 +110,110 @@ class ClockSampler:
                 "samples": len(clocks)}
 
 
-def build_inputs(w, device, rank=0, seed=20260001):
-    """Seeded synthetic vectors, queries, graph and entry points (of this rank's shard when sharded)."""
+def build_index(w, local, rank=0, seed=20260001, n_test=None):
+    """Seeded synthetic data of the workload and the index over it, built by the library on this GPU
+    (of this rank's shard when sharded).  Returns (dataset, index handle, build info)."""
     import torch
-    from coral_b200 import synth
+    from coral_b200 import capi, synth
     t0 = time.time()
     draw = seed + 1000 + rank if w.get("sharded") else None
-    if w["metric"] == "ip":
-        ds = synth.make_ip_cones(w["n"], w["train"], w["q"], dim=w["dim"], clusters=w["groups"], seed=seed,
-                                 device=device, draw_seed=draw)
-    else:
-        ds = synth.make_l2_mixture(w["n"], w["train"], w["q"], dim=w["dim"], centers=w["groups"], seed=seed,
-                                   device=device, draw_seed=draw)
-    g = synth.build_graph(ds.base, ds.train, ds.metric, max_degree=w["deg"], k_b=100, cell_size=512)
-    if device != "cpu":
-        torch.cuda.synchronize()
-    log(f"[bench] rank {rank}: inputs ready in {time.time() - t0:.1f}s")
+    cfg = synth.CONFIGS[w["data"]]
+    ds = synth.make_config(w["data"], w["train"], n_test or w["q"], n=w["n"], seed=seed, device=f"cuda:{local}",
+                           draw_seed=draw)
+    ix = capi.Index(w["n"], cfg["dim"], cfg["deg"], cfg["kind"], device=local)
+    ix.attach_vectors(ds.base)
+    t1 = time.time()
+    info = ix.build(ds.train, kb=100)
+    torch.cuda.synchronize()
+    info.update(data_s=round(t1 - t0, 1), build_s=round(time.time() - t1, 1), knn_tflops=round(ix.last_dense_tflops, 1))
+    log(f"[bench] rank {rank}: {w['data']} n={w['n']}: data {info['data_s']}s, build {info['build_s']}s "
+        f"({info['isolated']} isolated nodes enhanced)")
     ds.train = None
-    if device != "cpu":
-        torch.cuda.empty_cache()      # the builder's workspace is not part of the benchmark's footprint
-    return ds, g
+    torch.cuda.empty_cache()
+    return ds, ix, info
 
 
-def exact_topk(base, queries, k, metric):
-    """Exact ids and distances (fp32) of the k closest base rows: ground truth."""
-    import torch
-    from coral_b200 import synth
-    ids = synth.exact_knn(base, queries, k, metric)
-    rows = base[ids.long()]                                         # [Q, k, dim]
-    if metric == "ip":
-        d = (rows * queries[:, None, :]).sum(2)
-    else:
-        d = (rows - queries[:, None, :]).pow(2).sum(2)
-    return ids, d.to(torch.float32)
+def cpu_reference(base_h, adj_h, start_h, queries_h, gt_h, L0, k, max_L=1024, threads=0, repeat=1):
+    """The reference's CPU best-first search at the metric's recall: L is doubled from L0 until
+    recall@k on the ground-truth sample reaches 0.95 (the reference's own driver sweeps L the same
+    way, tests/test_search_pipeline.cpp:283-310).  Returns the report dict."""
+    from oracle import oracle
+    threads = threads or (os.cpu_count() or 1)
+    out, L = {}, L0
+    same_L = None
+    while True:
+        best = None
+        for _ in range(repeat):
+            ids, _, hops, secs, kind, used = oracle.cpu_search(base_h, adj_h, start_h, queries_h, L, k, threads=threads)
+            best = secs if best is None else min(best, secs)
+        m = min(len(queries_h), len(gt_h))
+        rec = oracle.recall(ids[:m], gt_h[:m], k)
+        row = {"L": L, "qps": len(queries_h) / best, "recall": rec, "seconds": best}
+        if same_L is None:
+            same_L = row
+        out = row
+        if rec >= 0.95 or L * 2 > max_L:
+            break
+        L *= 2
+    return {"value": out["qps"], "unit": "queries/s", "cores": used, "kind": kind, "L": out["L"], "recall": out["recall"],
+            "reached_recall_target": out["recall"] >= 0.95, "at_same_L": same_L,
+            "sample": (f"first {len(queries_h)} queries, k={k}, L doubled from {L0} until recall@{k} >= 0.95: L={out['L']}, "
+                       f"recall {out['recall']:.4f}, {out['seconds']:.2f}s per pass; "
+                       + ("reference NeighborPriorityQueue + AVX-512 DistanceL2 with the search_in_cpu loop restated"
+                          if kind == "reference" else "self-contained port of search_in_cpu"))}
 
 
 def run_reference(args, w, rank, world):
-    """The reference's CPU best-first search (src/search_in_cpu.cpp) on the host cores."""
+    """bench.py --impl reference: the reference's CPU search on this box's host cores, rank 0 only."""
     if rank != 0:
         return
     import torch
-    from oracle import oracle
-    device = "cuda" if torch.cuda.is_available() else "cpu"   # inputs are synthesised wherever it is fastest
-    ds, g = build_inputs(w, device)
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "reference", "unavailable": "the index for the CPU arm is built with the library's GPU "
+                          "builder; no CUDA device here"}), flush=True)
+        return
+    from coral_b200 import synth
+    ds, ix, info = build_index(w, 0)
+    k = w["k"]
     n_gt = min(2000, w["q"])
-    gt, _ = exact_topk(ds.base, ds.test[:n_gt], w["k"], w["metric"])
-    base, adj = ds.base.cpu().numpy(), g.adj.cpu().numpy()
-    start, test = g.start_ids.cpu().numpy(), ds.test.cpu().numpy()
-    gt = gt.cpu().numpy()
-    L = args.L or w["Ls"][0]
+    gt = ix.exact_knn(ds.test[:n_gt], k, dists=False)[0].cpu().numpy()
+    base, adj, start = ds.base.cpu().numpy(), ix.get_adjacency(), ix.get_start_ids()
+    test = ds.test.cpu().numpy()
+    ix.close()
     sample = min(args.cpu_queries, w["q"])
-    threads = os.cpu_count() or 1
-    times, rec, kind, used = [], None, "port", threads
+    L0 = args.L or w["Ls"][0]
+    reps = []
     for it in range(args.warmup + args.steps):
-        ids, _, hops, secs, kind, used = oracle.cpu_search(base, adj, start, test[:sample], L, w["k"], threads=threads)
+        r = cpu_reference(base, adj, start, test[:sample], gt, L0, k)
         if it >= args.warmup:
-            times.append(secs)
-        m = min(sample, gt.shape[0])
-        rec = oracle.recall(ids[:m], gt[:m], w["k"])
-    secs = sum(times) / len(times)
-    qps = sample / secs
-    desc = (f"first {sample} of {w['q']} queries per step, L={L}, k={w['k']}, recall@{w['k']}={rec:.4f}"
-            + (" on one shard" if w.get("sharded") else "") + "; "
-            + ("reference NeighborPriorityQueue + AVX-512 DistanceL2 with the search_in_cpu loop restated"
-               if kind == "reference" else "self-contained port of search_in_cpu"))
+            reps.append(r)
+    qps = sum(r["value"] for r in reps) / len(reps)
+    r = reps[-1]
+    cfg = synth.CONFIGS[w["data"]]
     out = {
         "impl": "reference", "metric": METRIC, "value": qps, "unit": "queries/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3, "higher_is_better": True,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sample / qps * 1e3, "higher_is_better": True,
         "scaling": "weak" if w.get("sharded") else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "n": w["n"], "dim": w["dim"], "metric": w["metric"], "max_degree": w["deg"],
-                   "queries_per_step": sample, "k": w["k"], "L": L, "recall": rec},
-        "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": used, "kind": kind, "sample": desc},
+        "config": {"workload": args.workload, "n": w["n"], "dim": cfg["dim"], "metric": cfg["kind"], "max_degree": cfg["deg"],
+                   "queries_per_step": sample, "k": k, "L": r["L"], "recall": r["recall"],
+                   "graph": "built by the library (k-NN lists -> NAP -> CE), the same graph as the GPU arm"},
+        "cpu_baseline": dict(r, value=qps),
         "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(out), flush=True)
 
 
-def run_latency(args, w, ix, ds, g, device, rank):
+def run_latency(args, w, ix, ds, device, rank):
     """Small-batch latency: per batch size, p50/p99 over many batches, device-resident (CUDA events
     around coral_search_async) and end to end (coral_search, pinned host queries in, host ids out)."""
     import numpy as np
     import torch
     from coral_b200 import capi, synth
-    L, k, dim = args.L or w["Ls"][0], w["k"], w["dim"]
+    cfg = synth.CONFIGS[w["data"]]
+    L, k, dim = args.L or w["Ls"][0], w["k"], cfg["dim"]
     lib, handle = capi.load(), ix._h
     n_gt = 2000
-    gt = synth.exact_knn(ds.base, ds.test[:n_gt], k, w["metric"])
+    gt = ix.exact_knn(ds.test[:n_gt], k, dists=False)[0]
     ids, _, _, _ = ix.search(ds.test[:n_gt], L, k, dists=False)
     recall = ix.count_hits(ids, gt, k) / float(k * n_gt)
     stream = torch.cuda.Stream(device=device)
@@ -236,14 +254,13 @@ def run_latency(args, w, ix, ds, g, device, rank):
         return table
 
     table = measure()
-    # The same batches with 10 % of the points deleted (tombstones only: the reference's deleted-bitset
-    # overload hides them from the results, src/search_gpu.cu:716; its topology repair and the insert
-    # path are not part of this build, so this is not the reference's "after delete + insert" state).
+    # The same batches with 10 % of the points deleted (tombstones: the reference's deleted-bitset
+    # overload hides them from the results, src/search_gpu.cu:716).
     rng = np.random.default_rng(77)
     dead = rng.random(w["n"]) < 0.10
     bits = np.packbits(dead, bitorder="little")
     bits = np.concatenate([bits, np.zeros((-len(bits)) % 4, np.uint8)]).view(np.uint32)
-    gt_wide = synth.exact_knn(ds.base, ds.test[:n_gt], 4 * k, w["metric"]).cpu().numpy()
+    gt_wide = ix.exact_knn(ds.test[:n_gt], 4 * k, dists=False)[0].cpu().numpy()
     gt_alive = np.stack([row[~dead[row]][:k] for row in gt_wide])
     ix.set_deleted(bits)
     ids_d, _, _, _ = ix.search(ds.test[:n_gt], L, k, dists=False)
@@ -257,14 +274,120 @@ def run_latency(args, w, ix, ds, g, device, rank):
         out = {"metric": "p50 latency of one query batch, 10Mx512 IP, L=%d" % L, "value": b1["p50_us"], "unit": "us",
                "n_gpus": 1, "steps": b1["batches"], "warmup": args.warmup, "ms_per_step": b1["p50_us"] * 1e-3,
                "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-               "config": {"workload": args.workload, "n": w["n"], "dim": dim, "metric": w["metric"], "max_degree": w["deg"],
+               "config": {"workload": args.workload, "n": w["n"], "dim": dim, "metric": cfg["kind"], "max_degree": cfg["deg"],
                           "k": k, "L": L, "recall": recall, "batch_sizes": w["latency"], "latency": table,
-                          "latency_with_10pct_deleted": table_deleted, "recall_with_10pct_deleted": recall_deleted,
+                          "latency_with_10pct_tombstones": table_deleted, "recall_with_10pct_tombstones": recall_deleted,
                           "l2_policy": "inputs larger than L2; every batch uses different queries"},
                "e2e": {"value": b1["e2e_p50_us"], "unit": "us", "h2d_bytes_per_step": dim * 4 * w["latency"][0],
                        "d2h_bytes_per_step": k * 4 * w["latency"][0] + 32},
                "gpu_launches": int(ix.launch_count - launches0)}
         print(json.dumps(out), flush=True)
+
+
+def quick_workload(name, local, steps=3, warmup=2):
+    """One small extra workload measured inside the default run: builds, picks the first configured
+    L with recall >= 0.95, times the device-resident search.  Returns a dict for config.extra."""
+    import numpy as np
+    import torch
+    from coral_b200 import capi, synth
+    w = WORKLOADS[name]
+    cfg = synth.CONFIGS[w["data"]]
+    ds, ix, info = build_index(w, local)
+    Q, k = w["q"], w["k"]
+    n_gt = min(2000, Q)
+    gt = ix.exact_knn(ds.test[:n_gt], k, dists=False)[0]
+    ix.prepare(Q, max(w["Ls"]), k)
+    out = {"build_s": info["build_s"], "by_L": {}}
+    peak, _ = measured_peak()
+    d_ids = torch.empty((Q, k), dtype=torch.int32, device=ds.test.device)
+    d_stats = torch.empty((Q, capi.STATS_W), dtype=torch.int32, device=ds.test.device)
+    stream = torch.cuda.Stream(device=ds.test.device)
+    chosen = None
+    for L in w["Ls"]:
+        ix.search_async(ds.test, L, k, d_ids, None, d_stats, stream.cuda_stream)
+        stream.synchronize()
+        rec = ix.count_hits(d_ids[:n_gt], gt, k) / float(k * n_gt)
+        st = d_stats.cpu().numpy().astype(np.int64)
+        alg = float((st[:, 1] * cfg["dim"] * 4 + st[:, 2] * ix.get_option("deg_pad") * 4 + cfg["dim"] * 4 + k * 8).sum())
+        for _ in range(warmup):
+            ix.search_async(ds.test, L, k, d_ids, None, None, stream.cuda_stream)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for _ in range(steps):
+            ix.search_async(ds.test, L, k, d_ids, None, None, stream.cuda_stream)
+        ev1.record(stream)
+        stream.synchronize()
+        ix.check()
+        ms = ev0.elapsed_time(ev1) / steps
+        out["by_L"][L] = {"qps": Q / (ms * 1e-3), "recall": rec, "alg_gbs": alg / (ms * 1e-3) / 1e9,
+                          "frac": alg / (ms * 1e-3) / 1e9 / peak}
+        if chosen is None and rec >= 0.95:
+            chosen = L
+    out["L"] = chosen
+    ix.close()
+    del ds
+    torch.cuda.empty_cache()
+    return out
+
+
+def sharded_check(local, rank, world, comm):
+    """A short sharded leg at the end of a replicated multi-GPU run: one 1M x 200 shard per GPU
+    (config 4's data), all queries on every shard, k = 100, L = 128, through coral_search_sharded.
+    Parity: the merged slice of every rank equals the CPU oracle's merge of the per-shard results
+    (checked on rank 0 for its own slice) and per-shard results equal the oracle's search."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from coral_b200 import sharded
+    from oracle import oracle
+    w = dict(data="c4", n=1_000_000, q=4_096, k=100, Ls=[128], train=100_000, sharded=True)
+    ds, ix, info = build_index(w, local, rank)
+    Q, k, L = w["q"], w["k"], 128
+    id_map = torch.from_numpy(sharded.interleaved_ids(w["n"], world, rank)).to(ds.test.device)
+    ix.prepare(Q, L, k)
+    sh = sharded.ShardedIndex(ix, id_map, comm)
+    stream = torch.cuda.Stream(device=ds.test.device)
+    torch.cuda.synchronize()
+    out_buf = None
+    for _ in range(2):
+        ids, d, lo, hi = sh.search(ds.test, L, k, stream.cuda_stream, out_buf)
+        out_buf = (ids, d)
+    stream.synchronize()
+    dist.barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    steps = 3
+    for _ in range(steps):
+        sh.search(ds.test, L, k, stream.cuda_stream, out_buf)
+    ev1.record(stream)
+    stream.synchronize()
+    ix.check()
+    ms = torch.tensor([ev0.elapsed_time(ev1) / steps], dtype=torch.float64, device=ds.test.device)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    # parity: every rank sends its local (global-id) results of a query sample to rank 0 through torch
+    sample = np.arange(lo, hi)[:64] if hi > lo else np.arange(0)
+    loc_ids, loc_d, _, _ = ix.search(ds.test, L, k)
+    gl = torch.where(loc_ids >= 0, id_map[loc_ids.clamp(min=0).long()], loc_ids)
+    all_ids = [torch.empty_like(gl) for _ in range(world)]
+    all_d = [torch.empty_like(loc_d) for _ in range(world)]
+    dist.all_gather(all_ids, gl)
+    dist.all_gather(all_d, loc_d)
+    ok = True
+    if len(sample):
+        o_ids, o_d = oracle.merge_shards(torch.stack(all_ids)[:, sample].cpu().numpy(),
+                                         torch.stack(all_d)[:, sample].cpu().numpy(), "l2")
+        mine_ids, mine_d = ids.cpu().numpy()[sample - lo], d.cpu().numpy()[sample - lo]
+        ok = bool(np.array_equal(mine_ids, o_ids) and np.array_equal(mine_d.view(np.uint32), o_d.view(np.uint32)))
+        # this shard's own search against the oracle on a few queries
+        base_h, adj_h, start_h = ds.base.cpu().numpy(), ix.get_adjacency(), ix.get_start_ids()
+        r_ids, r_d, _ = oracle.search(base_h, adj_h, start_h, ds.test[:16].cpu().numpy(), L, k, "l2")
+        ok = ok and bool(np.array_equal(loc_ids[:16].cpu().numpy(), r_ids))
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=ds.test.device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    ix.close()
+    return {"shards": world, "points_per_shard": w["n"], "queries": Q, "k": k, "L": L, "qps": Q / (float(ms.item()) * 1e-3),
+            "ms_per_step": float(ms.item()), "merged_equals_oracle_merge": bool(flag.item()),
+            "exchange": "one ncclAllGather of ids+distances, each rank merges its slice (coral_search_sharded)"}
 
 
 def main():
@@ -277,8 +400,9 @@ def main():
     ap.add_argument("--L", type=int, default=0, help="beam capacity; 0 = smallest configured L with recall >= 0.95")
     ap.add_argument("--queries", type=int, default=0, help="override the workload's query batch (profiling)")
     ap.add_argument("--n", type=int, default=0, help="override the number of base points (per shard)")
-    ap.add_argument("--cpu-queries", type=int, default=10000, help="query sample of the CPU baseline")
+    ap.add_argument("--cpu-queries", type=int, default=4000, help="query sample of the CPU baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the extra c1/c2 workloads and the sharded leg")
     ap.add_argument("--option", action="append", default=[], help="kernel tuning knob name=value")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
@@ -300,7 +424,7 @@ def main():
     import numpy as np
     import torch
     import torch.distributed as dist
-    from coral_b200 import capi, sharded
+    from coral_b200 import capi, sharded, synth
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the search path has no CPU fallback")
@@ -325,41 +449,32 @@ def main():
         dist.all_reduce(t, op=op)
         return float(t.item())
 
-    ds, g = build_inputs(w, device, rank)     # replicated: same seed on every rank; sharded: own shard
-    Q, k, dim = w["q"], w["k"], w["dim"]
-    if sharded_mode:
-        lo, hi = 0, Q                          # every shard searches every query
-        id_map = torch.from_numpy(sharded.interleaved_ids(w["n"], world, rank)).to(device)
-    else:
-        lo, hi = sharded.query_slice(Q, world, rank)
-        id_map = None
-    my_q = ds.test[lo:hi].contiguous()
-    nq = hi - lo
-    n_gt = min(2000, Q)
-
-    ix = capi.Index(w["n"], dim, w["deg"], w["metric"], device=local)
+    cfg = synth.CONFIGS[w["data"]]
+    ds, ix, build_info = build_index(w, local, rank)     # replicated: same seed on every rank; sharded: own shard
+    Q, k, dim = w["q"], w["k"], cfg["dim"]
     for kv in args.option:
         name, val = kv.split("=")
         ix.set_option(name, int(val))
-    ix.attach_vectors(ds.base)
-    ix.set_adjacency(g.adj)
-    ix.set_start_ids(g.start_ids)
-    ix.prepare(max(nq, n_gt), max(w["Ls"] + [args.L]), k)
+    n_gt = min(2000, Q)
+    comm = sharded.Communicator.from_torch(local) if world > 1 or sharded_mode else None
+    id_map = torch.from_numpy(sharded.interleaved_ids(w["n"], world, rank)).to(device) if sharded_mode else None
+    ix.prepare(Q, max(w["Ls"] + [args.L]), k)
     torch.cuda.synchronize()
-    sh = sharded.ShardedIndex(ix, id_map) if sharded_mode else None
+    sh = sharded.ShardedIndex(ix, id_map, comm) if sharded_mode else None
+    stream = torch.cuda.Stream(device=device)
 
     if w.get("latency"):
-        run_latency(args, w, ix, ds, g, device, rank)
+        run_latency(args, w, ix, ds, device, rank)
         ix.close()
         return
 
-    # ---- ground truth (exact, fp32) for the first n_gt queries; global across shards when sharded
-    gt_ids, gt_d = exact_topk(ds.base, ds.test[:n_gt], k, w["metric"])
+    # ---- ground truth (exact, tensor-core scan + exact re-rank) for the first n_gt queries; global when sharded
+    gt_ids, gt_d, _ = ix.exact_knn(ds.test[:n_gt], k)
     if sharded_mode:
         ix.map_ids(gt_ids, id_map)
         torch.cuda.synchronize()
         a_ids, a_d = sharded.all_gather_results(gt_ids, gt_d)
-        torch.cuda.synchronize()               # gathered on torch's streams, merged on the handle's
+        torch.cuda.synchronize()
         gt_ids, _ = ix.merge_shards(a_ids, a_d)
         torch.cuda.synchronize()
 
@@ -367,44 +482,61 @@ def main():
     recalls, L = {}, args.L
     for cand in ([args.L] if args.L else w["Ls"]):
         if sharded_mode:
-            ids, _ = sh.search(ds.test[:n_gt], cand, k)
+            ids, _, lo_, hi_ = sh.search(ds.test[:n_gt], cand, k)
+            torch.cuda.synchronize()
+            hits = torch.tensor([ix.count_hits(ids, gt_ids[lo_:hi_], k) if hi_ > lo_ else 0], dtype=torch.float64, device=device)
+            if world > 1:
+                dist.all_reduce(hits)
+            recalls[cand] = float(hits.item()) / float(k * n_gt)
         else:
             ids, _, _, _ = ix.search(ds.test[:n_gt], cand, k, dists=False)
-        recalls[cand] = ix.count_hits(ids, gt_ids, k) / float(k * n_gt)
+            recalls[cand] = ix.count_hits(ids, gt_ids, k) / float(k * n_gt)
         L = cand
         if recalls[cand] >= 0.95:
             break
     log(f"[bench] rank {rank}: recall by L {recalls}, using L={L}")
 
-    d_ids = torch.empty((nq, k), dtype=torch.int32, device=device)
-    d_dists = torch.empty((nq, k), dtype=torch.float32, device=device) if sharded_mode else None
+    # ---- this rank's part of the batch
+    if sharded_mode:
+        my_rows = None
+        my_q = ds.test
+        lo, hi = sharded.query_slice(Q, world, rank)
+        nq, n_out = Q, hi - lo
+    else:
+        if world > 1:
+            # every rank orders the whole batch (deterministic, identical everywhere) and takes its range
+            order = ix.query_order(ds.test)
+            torch.cuda.synchronize()
+            my_rows = sharded.sorted_slice(order, world, rank).long()
+            my_q = ds.test[my_rows].contiguous()
+        else:
+            my_rows = None
+            my_q = ds.test
+        nq = n_out = int(my_q.shape[0])
+
+    d_ids = torch.empty((n_out, k), dtype=torch.int32, device=device)
+    d_dists = torch.empty((n_out, k), dtype=torch.float32, device=device) if sharded_mode else None
     d_stats = torch.empty((nq, capi.STATS_W), dtype=torch.int32, device=device)
-    stream = torch.cuda.Stream(device=device)
     h_q = my_q.cpu().pin_memory()
-    h_ids = torch.empty((nq, k), dtype=torch.int32).pin_memory()
+    h_ids = torch.empty((n_out, k), dtype=torch.int32).pin_memory()
     h_q_np, h_ids_np = h_q.numpy(), h_ids.numpy()
     lib, handle = capi.load(), ix._h
-    merged = {}
-
-    def exchange_and_merge():
-        """Sharded tail of a step on `stream`: local->global ids, one all-gather, merge."""
-        ix.map_ids(d_ids, id_map, stream.cuda_stream)
-        with torch.cuda.stream(stream):        # buffers are allocated for, and used on, this stream
-            a_ids, a_d = sharded.all_gather_results(d_ids, d_dists)
-            merged["ids"], merged["dists"] = ix.merge_shards(a_ids, a_d, stream.cuda_stream)
 
     def device_step():
-        ix.search_async(my_q, L, k, d_ids, d_dists, None, stream.cuda_stream)
         if sharded_mode:
-            exchange_and_merge()
+            sh.search(my_q, L, k, stream.cuda_stream, (d_ids, d_dists))
+        else:
+            ix.search_async(my_q, L, k, d_ids, None, None, stream.cuda_stream)
 
     # ---- algorithmic bytes of one step (deterministic for the query set): untimed pass with counters
-    ix.search_async(my_q, L, k, d_ids, d_dists, d_stats, stream.cuda_stream)
+    scratch_ids = torch.empty((nq, k), dtype=torch.int32, device=device)
+    ix.search_async(my_q, L, k, scratch_ids, None, d_stats, stream.cuda_stream)
     stream.synchronize()
     ix.check()
     st = d_stats.cpu().numpy().astype(np.int64)
-    row_bytes, deg_pad = dim * 4, g.adj.shape[1]
+    row_bytes, deg_pad = dim * 4, ix.get_option("deg_pad")
     alg_bytes = float((st[:, 1] * row_bytes + st[:, 2] * deg_pad * 4 + row_bytes + k * 8).sum())
+    del scratch_ids
 
     # ---- device-resident timing
     for _ in range(args.warmup):
@@ -423,23 +555,27 @@ def main():
     ix.check()
     launches = ix.launch_count - launches0
     clocks = sampler.stop() if rank == 0 else None
-    dev_ms = reduce_ranks(ev0.elapsed_time(ev1), dist.ReduceOp.MAX) / args.steps
-    ref_ids = (merged["ids"] if sharded_mode else d_ids).cpu().numpy()
+    my_ms = ev0.elapsed_time(ev1) / args.steps
+    dev_ms = reduce_ranks(my_ms, dist.ReduceOp.MAX)
+    fastest_ms = reduce_ranks(my_ms, dist.ReduceOp.MIN)
+    ref_ids = d_ids.cpu().numpy()
 
-    # ---- end to end: pinned host queries in, host ids out, through coral_search
+    # ---- end to end: pinned host queries in, host ids out
     hops = C.c_int64(0)
 
     def e2e_step():
-        out_ptr = C.c_void_p(d_ids.data_ptr()) if sharded_mode else C.c_void_p(h_ids_np.ctypes.data)
-        rc = lib.coral_search(handle, C.c_void_p(h_q_np.ctypes.data), nq, L, k, out_ptr,
-                              C.c_void_p(d_dists.data_ptr()) if sharded_mode else None, None, C.byref(hops))
+        if sharded_mode:
+            with torch.cuda.stream(stream):
+                dq = h_q.to(device, non_blocking=True)
+            rc = lib.coral_search_sharded(handle, comm._c, C.c_void_p(id_map.data_ptr()), C.c_void_p(dq.data_ptr()), nq, L, k,
+                                          C.c_void_p(h_ids_np.ctypes.data), None, C.c_void_p(stream.cuda_stream))
+            if rc != 0:
+                raise RuntimeError(lib.coral_comm_last_error(comm._c).decode())
+            return
+        rc = lib.coral_search(handle, C.c_void_p(h_q_np.ctypes.data), nq, L, k, C.c_void_p(h_ids_np.ctypes.data),
+                              None, None, C.byref(hops))
         if rc != 0:
             raise RuntimeError(lib.coral_last_error(handle).decode())
-        if sharded_mode:
-            exchange_and_merge()
-            with torch.cuda.stream(stream):
-                h_ids.copy_(merged["ids"], non_blocking=True)
-            stream.synchronize()
 
     for _ in range(min(args.warmup, 2)):
         e2e_step()
@@ -454,54 +590,76 @@ def main():
 
     total_alg = reduce_ranks(alg_bytes, dist.ReduceOp.SUM)
     peak, peak_kind = measured_peak()
-    achieved = reduce_ranks(alg_bytes / (dev_ms * 1e-3) / 1e9, dist.ReduceOp.MIN)   # per GPU, against one GPU's peak
+    achieved = reduce_ranks(alg_bytes / (my_ms * 1e-3) / 1e9, dist.ReduceOp.MIN)   # per GPU, against one GPU's peak
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
-            from oracle import oracle
-            base_h, adj_h = ds.base.cpu().numpy(), g.adj.cpu().numpy()
             sample = min(args.cpu_queries, Q)
-            cids, _, chops, secs, kind, used = oracle.cpu_search(base_h, adj_h, g.start_ids.cpu().numpy(),
-                                                                  ds.test[:sample].cpu().numpy(), L, k)
-            m = min(sample, n_gt)
-            crec = oracle.recall(cids[:m], gt_ids[:m].cpu().numpy(), k)
-            cpu = {"value": sample / secs, "unit": "queries/s", "cores": used, "kind": kind,
-                   "sample": f"first {sample} of {Q} queries, L={L}, k={k}, recall@{k}={crec:.4f}, one pass of "
-                             f"{secs:.2f}s; search_in_cpu loop (always squared L2; best-first, so its recall on a "
-                             f"graph routed for full expansion differs)"}
-            del base_h, adj_h
+            cpu = cpu_reference(ds.base.cpu().numpy(), ix.get_adjacency(), ix.get_start_ids(), ds.test[:sample].cpu().numpy(),
+                                gt_ids[:min(sample, n_gt)].cpu().numpy(), L, k)
         except Exception as e:  # the baseline is a report, never a reason to lose the measurement
             cpu = {"value": None, "unit": "queries/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
 
+    index_gb = w["n"] * (row_bytes + deg_pad * 4) / 1e9
+    plan = {n_: ix.get_option(n_) for n_ in ("plan_stages", "plan_chunk_bytes", "plan_smem_bytes", "plan_hash_bits",
+                                               "plan_ctas_per_sm", "plan_warps")}
+    ix.close()
+    del ds
+    torch.cuda.empty_cache()
+
+    extra, shard_leg = None, None
+    if not args.no_extra and args.workload == "c3" and not args.queries and not args.n:
+        if world == 1:
+            extra = {}
+            for name in ("c2", "c1"):
+                try:
+                    extra[name] = quick_workload(name, local)
+                except Exception as e:
+                    extra[name] = {"failed": str(e)}
+        else:
+            try:
+                shard_leg = sharded_check(local, rank, world, comm)
+            except Exception as e:
+                shard_leg = {"failed": str(e)}
+
     if rank == 0:
-        index_gb = w["n"] * (row_bytes + deg_pad * 4) / 1e9
+        ratio = DRAM_PER_ALGORITHMIC_BYTE.get(args.workload)
         out = {
             "metric": METRIC, "value": Q / (dev_ms * 1e-3), "unit": "queries/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True,
             "scaling": "weak" if sharded_mode else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": args.workload, "n": w["n"] * (world if sharded_mode else 1), "dim": dim,
-                       "metric": w["metric"], "max_degree": w["deg"], "queries_per_step": Q, "k": k, "L": L,
-                       "recall": recalls[L], "recall_by_L": recalls, "entry_points": int(g.start_ids.numel()),
+                       "metric": cfg["kind"], "max_degree": cfg["deg"], "queries_per_step": Q, "k": k, "L": L,
+                       "recall": recalls[L], "recall_by_L": recalls, "entry_points": 16,
+                       "graph": "built in this run by the library: tensor-core exact k-NN lists of 100k training queries "
+                                "(k_b=100) -> NAP -> CE -> 16 FPS entry points",
+                       "build": build_info,
                        "parallelism": (f"{world} shards of {w['n']} points, all queries on every shard, one NCCL "
-                                       f"all-gather + merge" if sharded_mode else
-                                       f"replicated index, queries split x{world}"),
+                                       f"all-gather + slice merge" if sharded_mode else
+                                       f"replicated index, locality-ordered batch split x{world}"),
+                       "kernel_ms_per_rank": {"min": fastest_ms, "max": dev_ms},
                        "l2_policy": "inputs larger than L2 (index %.1f GB per GPU)" % index_gb,
-                       "plan": {n_: ix.get_option(n_) for n_ in ("plan_stages", "plan_chunk_bytes", "plan_smem_bytes",
-                                                                  "plan_hash_bits", "plan_ctas_per_sm", "plan_warps")}},
+                       "plan": plan, "extra_workloads": extra, "sharded_check": shard_leg},
             "e2e": {"value": Q / (e2e_ms * 1e-3), "unit": "queries/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": nq * dim * 4 * world, "d2h_bytes_per_step": (nq * k * 4 + 32) * world},
+                    "h2d_bytes_per_step": nq * dim * 4 * world, "d2h_bytes_per_step": (n_out * k * 4 + 32) * world},
             "gpu_launches": int(launches * world),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": peak_kind, "traffic": (MEASURED_TRAFFIC.get((args.workload, L))
-                                     if world == 1 and not args.queries and not args.n else None),
+                         "peak_source": peak_kind,
+                         "traffic": (ratio * alg_bytes if ratio and world == 1 else None),
+                         "traffic_source": ("profile constant: DRAM bytes per algorithmic byte from the ncu capture "
+                                            "summarised in profiles/, scaled to this launch" if ratio else None),
+                         "dram_frac": (ratio * achieved / peak if ratio else None),
                          "algorithmic_bytes_per_step": total_alg, "kernel": "beam_search_kernel",
-                         "note": "per GPU (slowest rank); algorithmic bytes = n_dist*dim*4 + n_exp*deg_pad*4 + dim*4 + k*8 per query"},
+                         "note": "per GPU (slowest rank); frac = ALGORITHMIC bytes (n_dist*dim*4 + n_exp*deg_pad*4 + dim*4 "
+                                 "+ k*8 per query) / time / measured copy peak -- part of those bytes is served by L2, "
+                                 "dram_frac = the DRAM share of it"},
             "cpu_baseline": cpu,
             "clocks": clocks,
         }
         print(json.dumps(out), flush=True)
-    ix.close()
+    if comm is not None:
+        comm.close()
     if world > 1:
         dist.destroy_process_group()
 

@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libcoral_b200.so")
 LIB_CHECKED = os.path.join(LIB_DIR, "libcoral_b200_checked.so")
-SOURCES = ["search_kernel.cu", "plan.cu", "dense_topk.cu", "build.cu", "schedule.cu", "capi.cu", "search_static.cu", "start_select.cu"]
+SOURCES = ["search_kernel.cu", "plan.cu", "dense_topk.cu", "build.cu", "schedule.cu", "capi.cu", "search_static.cu", "start_select.cu", "sharded.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--extended-lambda",
               "-Xcompiler", "-fPIC", "-shared"]
 
@@ -48,7 +48,7 @@ def build(force: bool = False, verbose: bool = False, checked: bool = False) -> 
         cmd += ["-DCORAL_CHECKED"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", lib, *[os.path.join(CSRC, s) for s in SOURCES]]
+    cmd += ["-o", lib, *[os.path.join(CSRC, s) for s in SOURCES], "-ldl"]
     env = dict(os.environ)
     env.pop("CC", None)   # nvcc should use the system host compiler
     env.pop("CXX", None)

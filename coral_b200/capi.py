@@ -22,12 +22,16 @@ EXPORTS = (
     "coral_version", "coral_compiled_sm", "coral_plan", "coral_index_create", "coral_index_destroy",
     "coral_index_set_vectors", "coral_index_attach_vectors", "coral_index_set_slots",
     "coral_index_set_adjacency", "coral_index_set_start_ids", "coral_index_select_start_ids",
+    "coral_index_get_adjacency", "coral_index_get_start_ids",
     "coral_index_set_deleted",
     "coral_search_prepare", "coral_search_free", "coral_search", "coral_search_async",
-    "coral_search_check", "coral_last_kernel_ms", "coral_last_total_ms", "coral_launch_count",
+    "coral_search_check", "coral_query_order", "coral_last_kernel_ms", "coral_last_total_ms", "coral_launch_count",
     "coral_set_option", "coral_get_option", "coral_count_hits", "coral_exact_knn", "coral_last_dense_ms",
     "coral_last_dense_flops", "coral_build_begin", "coral_build_nap", "coral_build_connect_enhance",
     "coral_build_get_graph", "coral_build_set_graph", "coral_build_end", "coral_merge_shards",
+    "coral_merge_shards_strided", "coral_comm_unique_id", "coral_comm_create", "coral_comm_create_all",
+    "coral_comm_destroy", "coral_comm_world", "coral_comm_rank", "coral_comm_last_error", "coral_query_slice",
+    "coral_search_sharded",
     "coral_map_ids", "coral_last_error", "coral_search_static", "coral_search_static_status",
 )
 
@@ -64,12 +68,15 @@ def load():
         "coral_index_set_adjacency": (C.c_int, [vp, i32p, C.c_int]),
         "coral_index_set_start_ids": (C.c_int, [vp, i32p, C.c_int]),
         "coral_index_select_start_ids": (C.c_int, [vp, C.c_int, C.c_int, i32p]),
+        "coral_index_get_adjacency": (C.c_int, [vp, i32p]),
+        "coral_index_get_start_ids": (C.c_int, [vp, i32p, C.c_int]),
         "coral_index_set_deleted": (C.c_int, [vp, vp]),
         "coral_search_prepare": (C.c_int, [vp, C.c_int, C.c_int, C.c_int]),
         "coral_search_free": (C.c_int, [vp]),
         "coral_search": (C.c_int, [vp, f32p, C.c_int, C.c_int, C.c_int, i32p, f32p, i32p, i64p]),
         "coral_search_async": (C.c_int, [vp, f32p, C.c_int, C.c_int, C.c_int, i32p, f32p, i32p, vp]),
         "coral_search_check": (C.c_int, [vp]),
+        "coral_query_order": (C.c_int, [vp, f32p, C.c_int, i32p, vp]),
         "coral_last_kernel_ms": (C.c_float, [vp]),
         "coral_last_total_ms": (C.c_float, [vp]),
         "coral_launch_count": (C.c_int64, [vp]),
@@ -87,6 +94,16 @@ def load():
         "coral_build_end": (C.c_int, [vp]),
         "coral_merge_shards": (C.c_int, [vp, i32p, f32p, C.c_int, C.c_int, C.c_int, i32p, f32p, vp]),
         "coral_map_ids": (C.c_int, [vp, i32p, C.c_int64, i32p, vp]),
+        "coral_merge_shards_strided": (C.c_int, [vp, i32p, f32p, C.c_int, C.c_int, C.c_int, C.c_int64, i32p, f32p, vp]),
+        "coral_comm_unique_id": (C.c_int, [vp]),
+        "coral_comm_create": (C.c_int, [C.POINTER(vp), C.c_int, C.c_int, C.c_int, vp]),
+        "coral_comm_create_all": (C.c_int, [C.POINTER(vp), C.POINTER(C.c_int), C.c_int]),
+        "coral_comm_destroy": (C.c_int, [vp]),
+        "coral_comm_world": (C.c_int, [vp]),
+        "coral_comm_rank": (C.c_int, [vp]),
+        "coral_comm_last_error": (C.c_char_p, [vp]),
+        "coral_query_slice": (None, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+        "coral_search_sharded": (C.c_int, [vp, vp, i32p, f32p, C.c_int, C.c_int, C.c_int, i32p, f32p, vp]),
         "coral_last_error": (C.c_char_p, [vp]),
         "coral_search_static": (C.c_int, [C.c_int, vp, f32p, i32p, C.c_int64, C.c_int, C.c_int, C.c_int, i32p, C.c_int,
                                           f32p, C.c_int, C.c_int, C.c_int, i32p, f32p]),
@@ -192,6 +209,25 @@ class Index:
                                                            C.c_void_p(out.ctypes.data)))
         return out
 
+    def get_adjacency(self):
+        """The installed adjacency as numpy int32 [n, deg_pad]."""
+        adj = np.empty((self.n, self.get_option("deg_pad")), np.int32)
+        self._check(self._lib.coral_index_get_adjacency(self._h, C.c_void_p(adj.ctypes.data)))
+        return adj
+
+    def get_adjacency_tensor(self, device):
+        """The installed adjacency as a CUDA int32 tensor [n, deg_pad] (device-to-device copy)."""
+        import torch
+        adj = torch.empty((self.n, self.get_option("deg_pad")), dtype=torch.int32, device=device)
+        self._check(self._lib.coral_index_get_adjacency(self._h, C.c_void_p(adj.data_ptr())))
+        return adj
+
+    def get_start_ids(self):
+        m = self._lib.coral_index_get_start_ids(self._h, None, 0)
+        out = np.empty(max(m, 0), np.int32)
+        self._lib.coral_index_get_start_ids(self._h, C.c_void_p(out.ctypes.data), int(out.size))
+        return out
+
     def set_deleted(self, bits):
         if bits is None:
             self._check(self._lib.coral_index_set_deleted(self._h, None))
@@ -257,6 +293,14 @@ class Index:
 
     def check(self):
         self._check(self._lib.coral_search_check(self._h))
+
+    def query_order(self, d_queries, stream=None):
+        """CUDA int32 tensor [Q]: the batch in the locality order (see coral_query_order)."""
+        import torch
+        order = torch.empty(int(d_queries.shape[0]), dtype=torch.int32, device=d_queries.device)
+        self._check(self._lib.coral_query_order(self._h, C.c_void_p(d_queries.data_ptr()), int(d_queries.shape[0]),
+                                                C.c_void_p(order.data_ptr()), C.c_void_p(stream) if stream else None))
+        return order
 
     @property
     def last_kernel_ms(self) -> float:
@@ -337,6 +381,22 @@ class Index:
 
     def build_end(self):
         self._check(self._lib.coral_build_end(self._h))
+
+    def build(self, train_queries, kb: int = 100, batch: int = 0, ce: bool = True, ce_L: int = 0,
+              ce_search_batch: int = 0, ce_nap_batch: int = 0, M: int = 0):
+        """The whole build over the handle's vectors, as IndexGPU::BuildGPU runs it
+        (src/index_gpu.cpp:308-383): exact k_b nearest base points of every training query, NAP in
+        batches, CE of the isolated nodes.  Leaves the graph and CE's entry points installed.
+        Returns a dict with the number of isolated nodes and uncertified k-NN rows."""
+        knn, _, bad = self.exact_knn(train_queries, kb, dists=False)
+        self.build_begin()
+        self.build_nap(knn, batch)
+        n_iso = self.build_connect_enhance(kb, ce_L, ce_search_batch, ce_nap_batch, M) if ce else 0
+        if not ce or n_iso == 0:
+            adj, _, deg = self.build_get_graph()
+            self.select_start_ids(int(np.nonzero(deg > 0)[0][0]), M or 16)
+        self.build_end()
+        return {"isolated": n_iso, "uncertified_knn": bad}
 
     def merge_shards(self, d_ids, d_dists, stream=None):
         """d_ids/d_dists: CUDA tensors [G,Q,k] -> merged CUDA tensors ([Q,k], [Q,k])."""

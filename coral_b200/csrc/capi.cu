@@ -51,6 +51,7 @@ struct Options {
     int probe_carry = 1;   // carry ids the first probe pair leaves open into the next scout step (0 = settle them at once)
     int gather = 0;        // row chunks to shared memory: 0 = one bulk copy per row chunk, 1 = 16-byte unit copies
     int schedule = 0;      // order large batches for L2 locality: 0 = automatic (batches >= 8192), 1 = always, -1 = never
+    int schedule_tc = 1;   // scheduling keys on the tensor cores (1) or by the fp32 SIMT tile kernel (0)
     int dense_passes = 3;  // tf32 passes of the dense scans behind coral_exact_knn: 3 = fp32-grade, 1 = plain tf32
 };
 
@@ -93,6 +94,10 @@ struct coral_index {
     int* d_keys = nullptr;
     int* d_bins = nullptr;
     int32_t* d_order = nullptr;
+    int* d_sort_scratch = nullptr;
+    void* d_sched_ws = nullptr;      // dense-scan workspace of the scheduling pre-pass
+    int sched_q_cap = 0, sched_split = 1;
+    int32_t* d_sched_ids = nullptr;  // [sched_q_cap] best frontier row of each query of a chunk
     int last_scheduled = 0;
     int last_plan_key = -1;   // plans[] key of the most recent search or prepare
     size_t cand_cap_alloc = 0;
@@ -232,8 +237,8 @@ __device__ __forceinline__ float unord32(uint32_t o, int metric) {
 // One warp per query: the G*k per-shard results are sorted by (distance, id) in
 // shared memory and the first k written out.
 __global__ void merge_shards_kernel(const int32_t* __restrict__ ids, const float* __restrict__ dists, int G,
-                                    int Q, int k, int n2, int metric, int32_t* __restrict__ ids_out,
-                                    float* __restrict__ dists_out) {
+                                    int Q, int k, long long g_stride, int n2, int metric,
+                                    int32_t* __restrict__ ids_out, float* __restrict__ dists_out) {
     extern __shared__ unsigned long long msm[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     unsigned long long* s = msm + (size_t)warp * n2;
@@ -242,7 +247,7 @@ __global__ void merge_shards_kernel(const int32_t* __restrict__ ids, const float
             unsigned long long key = ~0ull;
             if (i < G * k) {
                 const int g = i / k, j = i - g * k;
-                const size_t o = ((size_t)g * Q + q) * k + j;
+                const size_t o = (size_t)g * g_stride + (size_t)q * k + j;
                 const int id = ids[o];
                 if (id >= 0) key = ((unsigned long long)ord32(dists[o], metric) << 32) | (uint32_t)id;
             }
@@ -298,6 +303,9 @@ void free_search(coral_index* h) {
     cudaFree(h->d_keys);    h->d_keys = nullptr;
     cudaFree(h->d_bins);    h->d_bins = nullptr;
     cudaFree(h->d_order);   h->d_order = nullptr;
+    cudaFree(h->d_sort_scratch); h->d_sort_scratch = nullptr;
+    cudaFree(h->d_sched_ws);     h->d_sched_ws = nullptr;
+    cudaFree(h->d_sched_ids);    h->d_sched_ids = nullptr;
     cudaFree(h->d_queries); h->d_queries = nullptr;
     cudaFree(h->d_ids);     h->d_ids = nullptr;
     cudaFree(h->d_dists);   h->d_dists = nullptr;
@@ -490,6 +498,22 @@ int coral_index_set_start_ids(coral_index_t* h, const int32_t* ids, int M) {
     return CORAL_OK;
 }
 
+int coral_index_get_adjacency(coral_index_t* h, int32_t* adj_out) {
+    if (!h || !adj_out) return fail(h, CORAL_ERR_ARG, "null argument");
+    if (!h->d_adj) return fail(h, CORAL_ERR_STATE, "no adjacency set");
+    if (int rc = ensure_device(h)) return rc;
+    CK(cudaMemcpyAsync(adj_out, h->d_adj, (size_t)h->n * h->deg_pad * sizeof(int32_t), cudaMemcpyDefault, h->stream));
+    CK(cudaStreamSynchronize(h->stream));
+    return CORAL_OK;
+}
+
+int coral_index_get_start_ids(coral_index_t* h, int32_t* ids_out, int capacity) {
+    if (!h) return -1;
+    if (ids_out)
+        for (int i = 0; i < h->M && i < capacity; ++i) ids_out[i] = h->h_start[(size_t)i];
+    return h->M;
+}
+
 int coral_index_select_start_ids(coral_index_t* h, int first_id, int M, int32_t* ids_out) {
     if (!h || M <= 0 || M > 4096) return fail(h, CORAL_ERR_ARG, "select start ids: need 1..4096 ids");
     if (first_id < 0 || (int64_t)first_id >= h->n) return fail(h, CORAL_ERR_ARG, "first id out of range");
@@ -544,6 +568,7 @@ int coral_set_option(coral_index_t* h, const char* name, int value) {
     else if (s == "gather") o.gather = value;
     else if (s == "probe_carry") o.probe_carry = value;
     else if (s == "dense_passes") o.dense_passes = value;
+    else if (s == "schedule_tc") o.schedule_tc = value;
     else return fail(h, CORAL_ERR_ARG, "unknown option " + s);
     h->plans.clear();
     return CORAL_OK;
@@ -567,6 +592,7 @@ int coral_get_option(coral_index_t* h, const char* name, int* value) {
     else if (s == "gather") *value = o.gather;
     else if (s == "probe_carry") *value = o.probe_carry;
     else if (s == "dense_passes") *value = o.dense_passes;
+    else if (s == "schedule_tc") *value = o.schedule_tc;
     else if (s == "sort_tile") *value = o.sort_tile;
     else if (s == "scout_ids") *value = o.scout_ids;
     else if (s == "visit_cache_bits") *value = o.visit_cache_bits;
@@ -628,6 +654,15 @@ int coral_search_prepare(coral_index_t* h, int max_queries, int max_L, int max_k
     CK(cudaMalloc(&h->d_keys, (size_t)max_queries * sizeof(int)));
     CK(cudaMalloc(&h->d_order, (size_t)max_queries * sizeof(int32_t)));
     CK(cudaMalloc(&h->d_bins, (size_t)kMaxFrontier * sizeof(int)));
+    CK(cudaMalloc(&h->d_sort_scratch, coral::sort_scratch_ints(max_queries, kMaxFrontier) * sizeof(int)));
+    if (h->opt.schedule >= 0 && max_queries >= 4096 && h->opt.schedule_tc != 0) {
+        // tensor-core pre-pass: queries in chunks of one CTA per SM, the frontier as the "base"
+        h->sched_q_cap = std::min(max_queries, h->sm_count * coral::kDenseTileM);
+        const int q_tiles = (h->sched_q_cap + coral::kDenseTileM - 1) / coral::kDenseTileM;
+        h->sched_split = std::max(1, std::min(kMaxFrontier / coral::kDenseTileN, h->sm_count / q_tiles));
+        CK(cudaMalloc(&h->d_sched_ws, coral::dense_workspace_bytes(h->sched_q_cap, kMaxFrontier, h->dim, h->sched_split)));
+        CK(cudaMalloc(&h->d_sched_ids, (size_t)h->sched_q_cap * sizeof(int32_t)));
+    }
     CK(cudaMalloc(&h->d_queries, (size_t)max_queries * h->dim * sizeof(float)));
     CK(cudaMalloc(&h->d_ids, (size_t)max_queries * max_k * sizeof(int32_t)));
     CK(cudaMalloc(&h->d_dists, (size_t)max_queries * max_k * sizeof(float)));
@@ -669,6 +704,36 @@ static int ensure_frontier(coral_index* h) {
     h->launches += 1;
     CK(cudaStreamSynchronize(h->stream));
     h->n_front = (int)ids.size();
+    return CORAL_OK;
+}
+
+// h->d_order[0..Q) <- the batch ordered by each query's closest frontier row.  The scores are formed
+// on the tensor cores (one tf32 pass of the dense scan, the 8 best re-ranked exactly, so the key is
+// the exact nearest frontier row and does not depend on tensor-core rounding); option
+// "schedule_tc" = 0 selects the fp32 SIMT tile kernel instead.
+static int query_order(coral_index* h, const float* d_queries, int Q, cudaStream_t st) {
+    if (h->d_sched_ws && h->opt.schedule_tc != 0) {
+        coral::DenseWorkspace w;
+        coral::dense_workspace_carve(h->d_sched_ws, h->sched_q_cap, kMaxFrontier, h->dim, h->sched_split, w);
+        const int keep = 8;
+        for (int q0 = 0; q0 < Q; q0 += h->sched_q_cap) {
+            const int nq = std::min(h->sched_q_cap, Q - q0);
+            const float* q = d_queries + (size_t)q0 * h->dim;
+            CK(coral::dense_begin(w, q, nq, h->dim, st, &h->launches));
+            CK(coral::dense_scan_chunk(w, q, nq, h->d_front_vecs, 0, h->n_front, h->dim, h->metric, 1, keep, h->sm_count, st,
+                                       &h->launches));
+            CK(coral::dense_finish(w, q, nq, h->d_front_vecs, h->dim, h->metric, 1, keep, 1, h->d_sched_ids, nullptr, nullptr,
+                                   st, &h->launches));
+            CK(coral::keys_from_ids(h->d_sched_ids, nq, 1, h->n_front, h->d_keys + q0, h->sm_count, st));
+            h->launches += 1;
+        }
+    } else {
+        CK(coral::frontier_keys_simt(d_queries, Q, h->dim, h->metric, h->d_front_vecs, h->d_front_norm, h->n_front, h->d_keys,
+                                     st));
+        h->launches += 1;
+    }
+    CK(coral::sort_queries_by_key(h->d_keys, Q, h->n_front, h->d_bins, h->d_sort_scratch, h->d_order, h->sm_count, st));
+    h->launches += 4;
     return CORAL_OK;
 }
 
@@ -750,9 +815,7 @@ static int enqueue_search(coral_index* h, const float* d_queries, int Q, int L, 
     if (cs == 1 && h->opt.schedule >= 0 && (h->opt.schedule > 0 || Q >= 8192)) {
         if (int rc = ensure_frontier(h)) return rc;
         if (h->n_front >= 2) {
-            CK(coral::schedule_queries(d_queries, Q, h->dim, h->metric, h->d_front_vecs, h->d_front_norm, h->n_front,
-                                       h->d_keys, h->d_bins, h->d_order, h->sm_count, st));
-            h->launches += 4;
+            if (int rc = query_order(h, d_queries, Q, st)) return rc;
             a.order = h->d_order;
             h->last_scheduled = 1;
         }
@@ -770,6 +833,19 @@ int coral_search_async(coral_index_t* h, const float* d_queries, int Q, int L, i
     if (int rc = ensure_device(h)) return rc;
     cudaStream_t st = stream ? (cudaStream_t)stream : h->stream;
     return enqueue_search(h, d_queries, Q, L, k, d_ids_out, d_dists_out, d_stats_out, st);
+}
+
+int coral_query_order(coral_index_t* h, const float* d_queries, int Q, int32_t* d_order_out, void* stream) {
+    if (!h || !d_queries || !d_order_out || Q <= 0) return fail(h, CORAL_ERR_ARG, "bad argument");
+    if (!h->prepared) return fail(h, CORAL_ERR_STATE, "coral_search_prepare has not been called");
+    if (Q > h->max_q) return fail(h, CORAL_ERR_LIMIT, "request exceeds coral_search_prepare sizes");
+    if (int rc = ensure_device(h)) return rc;
+    cudaStream_t st = stream ? (cudaStream_t)stream : h->stream;
+    if (int rc = ensure_frontier(h)) return rc;
+    if (h->n_front < 2) return fail(h, CORAL_ERR_STATE, "no frontier to order by (more than 64 entry points, or no edges)");
+    if (int rc = query_order(h, d_queries, Q, st)) return rc;
+    CK(cudaMemcpyAsync(d_order_out, h->d_order, (size_t)Q * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
+    return CORAL_OK;
 }
 
 int coral_search_check(coral_index_t* h) {
@@ -1146,7 +1222,13 @@ int coral_build_end(coral_index_t* h) {
 
 int coral_merge_shards(coral_index_t* h, const int32_t* d_ids, const float* d_dists, int G, int Q, int k,
                        int32_t* d_ids_out, float* d_dists_out, void* stream) {
-    if (!h || !d_ids || !d_dists || !d_ids_out || !d_dists_out || G <= 0 || Q < 0 || k <= 0)
+    return coral_merge_shards_strided(h, d_ids, d_dists, G, Q, k, (int64_t)Q * k, d_ids_out, d_dists_out, stream);
+}
+
+int coral_merge_shards_strided(coral_index_t* h, const int32_t* d_ids, const float* d_dists, int G, int Q, int k,
+                               int64_t shard_stride, int32_t* d_ids_out, float* d_dists_out, void* stream) {
+    if (!h || !d_ids || !d_dists || !d_ids_out || !d_dists_out || G <= 0 || Q < 0 || k <= 0 ||
+        shard_stride < (int64_t)Q * k)
         return fail(h, CORAL_ERR_ARG, "bad argument");
     if ((long long)G * k > 4096) return fail(h, CORAL_ERR_LIMIT, "G*k must not exceed 4096");
     if (int rc = ensure_device(h)) return rc;
@@ -1157,7 +1239,8 @@ int coral_merge_shards(coral_index_t* h, const int32_t* d_ids, const float* d_di
     const size_t smem = (size_t)wpb * n2 * 8;
     CK(cudaFuncSetAttribute(merge_shards_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int blocks = std::min((Q + wpb - 1) / wpb, h->sm_count * 8);
-    merge_shards_kernel<<<blocks, wpb * 32, smem, st>>>(d_ids, d_dists, G, Q, k, n2, h->metric, d_ids_out, d_dists_out);
+    merge_shards_kernel<<<blocks, wpb * 32, smem, st>>>(d_ids, d_dists, G, Q, k, (long long)shard_stride, n2, h->metric,
+                                                        d_ids_out, d_dists_out);
     h->launches += 1;
     CK(cudaGetLastError());
     return CORAL_OK;

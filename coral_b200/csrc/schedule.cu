@@ -8,9 +8,11 @@
 // node re-read each other's rows from the 126 MB L2 instead of from HBM.
 //
 // So before a large batch is searched: (1) one dense pass, queries x frontier
-// vectors, keeps the best frontier node per query (fp32 SIMT tiles; it only
-// orders the work, so its rounding never reaches a result), (2) a counting sort
-// by that node yields the order in which the persistent CTAs take the queries.
+// vectors, keeps the best frontier node per query -- on the tensor cores (the
+// tcgen05 scan of dense_topk.cu, one tf32 pass, exact re-rank of the 8 best), with
+// the fp32 SIMT tile kernel below as the variant for comparison; the key only
+// orders the work, so nothing of it reaches a result -- (2) a stable counting
+// sort by that node yields the order in which the persistent CTAs take the queries.
 // Results are written at each query's own position: nothing observable changes
 // except speed (10M x 512, 100k queries, L=64: 422k -> 492k queries/s).
 #include <cuda_runtime.h>
@@ -125,8 +127,38 @@ __global__ void gather_frontier_kernel(const float* __restrict__ vecs, const int
     }
 }
 
-__global__ void histogram_kernel(const int* __restrict__ keys, int Q, int* __restrict__ bins) {
-    for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < Q; q += gridDim.x * blockDim.x) atomicAdd(&bins[keys[q]], 1);
+// ---- deterministic counting sort of the batch by key (stable: equal keys keep their query order,
+// so every GPU that sorts the same batch gets the same order).
+constexpr int kSortChunk = 1024;
+
+// One block per chunk of 1024 queries: rank of every query among the chunk's earlier queries with
+// the same key, and the chunk's count per key.
+__global__ void __launch_bounds__(kSortChunk) chunk_rank_kernel(const int* __restrict__ keys, int Q, int F,
+                                                                int* __restrict__ rank_in_chunk,
+                                                                int* __restrict__ chunk_counts) {
+    __shared__ int sk[kSortChunk];
+    const int q = blockIdx.x * kSortChunk + threadIdx.x;
+    const int key = q < Q ? keys[q] : -1;
+    sk[threadIdx.x] = key;
+    __syncthreads();
+    if (q >= Q) return;
+    int r = 0;
+    for (int i = 0; i < (int)threadIdx.x; ++i) r += sk[i] == key;
+    rank_in_chunk[q] = r;
+    atomicAdd(&chunk_counts[(size_t)blockIdx.x * F + key], 1);
+}
+
+// One thread per key: chunk_counts[c][key] -> exclusive prefix over the chunks; bins[key] = total.
+__global__ void column_scan_kernel(int* __restrict__ chunk_counts, int n_chunks, int F, int* __restrict__ bins) {
+    const int key = blockIdx.x * blockDim.x + threadIdx.x;
+    if (key >= F) return;
+    int run = 0;
+    for (int c = 0; c < n_chunks; ++c) {
+        const int v = chunk_counts[(size_t)c * F + key];
+        chunk_counts[(size_t)c * F + key] = run;
+        run += v;
+    }
+    bins[key] = run;
 }
 
 // One block: bins[0..F) -> exclusive prefix in place.
@@ -153,9 +185,20 @@ __global__ void exclusive_scan_kernel(int* __restrict__ bins, int F) {
     }
 }
 
-__global__ void scatter_kernel(const int* __restrict__ keys, int Q, int* __restrict__ offsets, int32_t* __restrict__ order) {
-    for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < Q; q += gridDim.x * blockDim.x)
-        order[atomicAdd(&offsets[keys[q]], 1)] = q;
+__global__ void place_kernel(const int* __restrict__ keys, int Q, int F, const int* __restrict__ bins,
+                             const int* __restrict__ chunk_counts, const int* __restrict__ rank_in_chunk,
+                             int32_t* __restrict__ order) {
+    for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < Q; q += gridDim.x * blockDim.x) {
+        const int key = keys[q];
+        order[bins[key] + chunk_counts[(size_t)(q / kSortChunk) * F + key] + rank_in_chunk[q]] = q;
+    }
+}
+
+__global__ void first_column_kernel(const int32_t* __restrict__ ids, int Q, int stride, int F, int* __restrict__ keys) {
+    for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < Q; q += gridDim.x * blockDim.x) {
+        const int v = ids[(size_t)q * stride];
+        keys[q] = v >= 0 && v < F ? v : 0;
+    }
 }
 
 }  // namespace
@@ -166,15 +209,35 @@ cudaError_t gather_frontier(const float* vecs, const int32_t* d_ids, int F, int 
     return cudaGetLastError();
 }
 
-cudaError_t schedule_queries(const float* d_queries, int Q, int dim, int metric, const float* fvecs, const float* fnorm,
-                             int F, int* d_keys, int* d_bins, int32_t* d_order, int sm_count, cudaStream_t stream) {
-    cudaError_t e = cudaMemsetAsync(d_bins, 0, (size_t)F * sizeof(int), stream);
+size_t sort_scratch_ints(int Q, int F) {
+    const size_t chunks = (size_t)(Q + kSortChunk - 1) / kSortChunk;
+    return (size_t)Q + chunks * (size_t)F;
+}
+
+cudaError_t sort_queries_by_key(const int* d_keys, int Q, int F, int* d_bins, int* d_scratch, int32_t* d_order,
+                                int sm_count, cudaStream_t stream) {
+    const int n_chunks = (Q + kSortChunk - 1) / kSortChunk;
+    int* rank_in_chunk = d_scratch;
+    int* chunk_counts = d_scratch + Q;
+    cudaError_t e = cudaMemsetAsync(chunk_counts, 0, (size_t)n_chunks * F * sizeof(int), stream);
     if (e != cudaSuccess) return e;
-    frontier_argmax_kernel<<<(Q + kTileQ - 1) / kTileQ, 256, 0, stream>>>(d_queries, Q, dim, fvecs, fnorm, F, metric, d_keys);
-    const int blocks = sm_count * 4 < (Q + 255) / 256 ? sm_count * 4 : (Q + 255) / 256;
-    histogram_kernel<<<blocks, 256, 0, stream>>>(d_keys, Q, d_bins);
+    chunk_rank_kernel<<<n_chunks, kSortChunk, 0, stream>>>(d_keys, Q, F, rank_in_chunk, chunk_counts);
+    column_scan_kernel<<<(F + 255) / 256, 256, 0, stream>>>(chunk_counts, n_chunks, F, d_bins);
     exclusive_scan_kernel<<<1, 1024, 0, stream>>>(d_bins, F);
-    scatter_kernel<<<blocks, 256, 0, stream>>>(d_keys, Q, d_bins, d_order);
+    const int blocks = sm_count * 4 < (Q + 255) / 256 ? sm_count * 4 : (Q + 255) / 256;
+    place_kernel<<<blocks, 256, 0, stream>>>(d_keys, Q, F, d_bins, chunk_counts, rank_in_chunk, d_order);
+    return cudaGetLastError();
+}
+
+cudaError_t keys_from_ids(const int32_t* d_ids, int Q, int stride, int F, int* d_keys, int sm_count, cudaStream_t stream) {
+    const int blocks = sm_count * 4 < (Q + 255) / 256 ? sm_count * 4 : (Q + 255) / 256;
+    first_column_kernel<<<blocks, 256, 0, stream>>>(d_ids, Q, stride, F, d_keys);
+    return cudaGetLastError();
+}
+
+cudaError_t frontier_keys_simt(const float* d_queries, int Q, int dim, int metric, const float* fvecs, const float* fnorm,
+                               int F, int* d_keys, cudaStream_t stream) {
+    frontier_argmax_kernel<<<(Q + kTileQ - 1) / kTileQ, 256, 0, stream>>>(d_queries, Q, dim, fvecs, fnorm, F, metric, d_keys);
     return cudaGetLastError();
 }
 

@@ -8,9 +8,12 @@ Two modes, as the search path allows (the reference itself is single-GPU):
   and entry points and searches ALL queries; the per-shard top-k (global ids, distances)
   are exchanged with ONE all-gather and merged per query by (distance, id).
 
-`torch.distributed` is the plumbing (NCCL on GPUs, gloo in the CPU tests); the merge runs in
-the library's shard-merge kernel on GPUs.  The search itself is injected (`search_fn`) so the
-exchange logic can be exercised on CPU ranks with any local searcher.
+On GPUs the whole sharded step is ONE call into the C library (`coral_search_sharded`: local
+search, id mapping, one ncclAllGather on the caller's stream, merge of this rank's slice of the
+batch); `Communicator` only carries the NCCL unique id from rank 0 to the others through
+`torch.distributed`.  The pure-Python `sharded_search` states the same exchange over any
+`torch.distributed` backend with an injected local searcher, so that the logic can be exercised
+on CPU ranks (gloo).
 """
 from __future__ import annotations
 
@@ -78,26 +81,86 @@ def sharded_search(search_fn: Callable, id_map, queries, L: int, k: int, merge_f
     return merge_fn(all_ids, all_dists)
 
 
+def sorted_slice(order: torch.Tensor, world: int, rank: int) -> torch.Tensor:
+    """Rows of the batch `rank` searches when the index is replicated and the batch has been ordered
+    for locality (`order[i]` = the i-th query to run): the rank-th contiguous range of the ORDERED
+    batch, so every GPU sees 1/world of the graph regions at full multiplicity instead of all of
+    them thinly.  Returns the original row numbers (results go back to those rows)."""
+    lo, hi = query_slice(int(order.numel()), world, rank)
+    return order[lo:hi]
+
+
+class Communicator:
+    """The library's NCCL communicator (coral_comm_*), one per process and GPU."""
+
+    def __init__(self, device: int, world: int, rank: int, unique_id: bytes):
+        import ctypes as C
+        from . import capi
+        self._lib = capi.load()
+        self._c = C.c_void_p()
+        buf = C.create_string_buffer(unique_id, 128)
+        rc = self._lib.coral_comm_create(C.byref(self._c), int(device), int(world), int(rank), buf)
+        if rc != 0:
+            raise capi.CoralError(rc, self._lib.coral_comm_last_error(None).decode())
+        self.world, self.rank, self.device = world, rank, device
+
+    @staticmethod
+    def unique_id() -> bytes:
+        import ctypes as C
+        from . import capi
+        lib = capi.load()
+        buf = C.create_string_buffer(128)
+        rc = lib.coral_comm_unique_id(buf)
+        if rc != 0:
+            raise capi.CoralError(rc, lib.coral_comm_last_error(None).decode())
+        return buf.raw
+
+    @classmethod
+    def from_torch(cls, device: int, group=None) -> "Communicator":
+        """Collective: rank 0 makes the unique id, torch.distributed carries it to the others."""
+        if not dist.is_initialized() or dist.get_world_size(group) == 1:
+            return cls(device, 1, 0, cls.unique_id())
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        box = [cls.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0, group=group)
+        return cls(device, world, rank, box[0])
+
+    def close(self):
+        if self._c:
+            self._lib.coral_comm_destroy(self._c)
+            import ctypes as C
+            self._c = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class ShardedIndex:
-    """A shard's index handle plus its local->global id map, searched collectively."""
+    """A shard's index handle, its local->global id map and the communicator, searched collectively."""
 
-    def __init__(self, index, id_map: torch.Tensor, group=None):
-        self.index, self.id_map, self.group = index, id_map.to(torch.int32).contiguous(), group
+    def __init__(self, index, id_map: torch.Tensor, comm: Communicator):
+        self.index, self.comm = index, comm
+        self.id_map = id_map.to(torch.int32).contiguous() if id_map is not None else None
 
-    def search(self, queries: torch.Tensor, L: int, k: int):
-        """queries: CUDA tensor [Q, dim], the same on every rank.  Returns merged (ids, dists)."""
-        def local(q, L_, k_):
-            ids, dists, _, _ = self.index.search(q, L_, k_, dists=True)
-            return ids, dists
-
-        def mapper(ids, id_map):
-            self.index.map_ids(ids, id_map)
-            torch.cuda.synchronize()
-
-        def merger(all_ids, all_dists):
-            torch.cuda.synchronize()       # the gathered buffers were produced on torch's streams,
-            out = self.index.merge_shards(all_ids, all_dists)   # the merge runs on the handle's
-            torch.cuda.synchronize()
-            return out
-
-        return sharded_search(local, self.id_map, queries, L, k, merger, mapper, self.group)
+    def search(self, queries: torch.Tensor, L: int, k: int, stream=None, out=None):
+        """queries: CUDA tensor [Q, dim], the same on every rank.  Enqueues the whole step on `stream`
+        (an int cudaStream_t; None = the legacy default stream) and returns this rank's slice of the
+        merged batch: (ids[hi-lo, k], dists[hi-lo, k], lo, hi), CUDA tensors (`out` = a reusable pair)."""
+        import ctypes as C
+        from . import capi
+        Q = int(queries.shape[0])
+        lo, hi = query_slice(Q, self.comm.world, self.comm.rank)
+        if out is None:
+            out = (torch.empty((hi - lo, k), dtype=torch.int32, device=queries.device),
+                   torch.empty((hi - lo, k), dtype=torch.float32, device=queries.device))
+        ids, dists = out
+        rc = self.index._lib.coral_search_sharded(
+            self.index._h, self.comm._c, C.c_void_p(self.id_map.data_ptr()) if self.id_map is not None else None,
+            C.c_void_p(queries.data_ptr()), Q, L, k, C.c_void_p(ids.data_ptr()), C.c_void_p(dists.data_ptr()),
+            C.c_void_p(stream) if stream else None)
+        if rc != 0:
+            raise capi.CoralError(rc, self.index._lib.coral_comm_last_error(self.comm._c).decode())
+        return ids, dists, lo, hi

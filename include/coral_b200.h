@@ -108,6 +108,13 @@ int coral_index_set_start_ids(coral_index_t* h, const int32_t* ids, int M);
  * freed before returning. */
 int coral_index_select_start_ids(coral_index_t* h, int first_id, int M, int32_t* ids_out);
 
+/* Reads the installed graph back: adjacency [n][deg_pad] to a host or device buffer (replaces the
+ * device-to-host copy of Graph::write_back_all_gpu_slots behind save_build, include/graph.cuh:481),
+ * and the entry points (returns how many are installed; copies at most `capacity` to ids_out, which
+ * may be NULL) as Graph::get_start_ids does (include/graph.cuh:494). */
+int coral_index_get_adjacency(coral_index_t* h, int32_t* adj_out);
+int coral_index_get_start_ids(coral_index_t* h, int32_t* ids_out, int capacity);
+
 /* Replaces d_deleted (src/search_gpu.cu:582-833, :716): bit i set = node i is
  * skipped when the final top-k is written.  Host pointer to (n+31)/32 words, or
  * NULL to clear. */
@@ -135,6 +142,16 @@ int coral_search(coral_index_t* h, const float* queries, int Q, int L, int k, in
  * call returns without synchronising.  Check coral_search_check afterwards. */
 int coral_search_async(coral_index_t* h, const float* d_queries, int Q, int L, int k,
                        int32_t* d_ids_out, float* d_dists_out, int32_t* d_stats_out, void* stream);
+
+/* The order in which a large batch is run for locality: d_order_out[i] (device, Q ints) = the row of
+ * the i-th query to run, the batch sorted by each query's closest neighbour of the entry points,
+ * equal keys in row order (deterministic: every GPU that orders the same batch over the same
+ * replicated index gets the same order, so rank r of a replicated multi-GPU search can take the
+ * r-th contiguous range of the ORDERED batch and see 1/world of the graph at full multiplicity).
+ * The query x frontier scores are the dense contraction of this path and run on the tensor cores
+ * (replaces nothing in the reference, whose warp_calc_dist seeds one start node per warp,
+ * src/search_gpu.cu:14-23).  Enqueued on `stream` (NULL = the handle's), no synchronisation. */
+int coral_query_order(coral_index_t* h, const float* d_queries, int Q, int32_t* d_order_out, void* stream);
 
 /* After the stream has been synchronised: CORAL_ERR_KERNEL if the last launch
  * reported a bounded wait that ran out, else CORAL_OK. */
@@ -167,6 +184,7 @@ int64_t coral_launch_count(coral_index_t* h);
  *   "max_rounds"             per-query round limit (status 3 when reached)
  *   "cluster_size"           CTAs that share one query when the batch is far smaller than the GPU:
  *                            0 = automatic, 1 = never, 2/4/8/16 = forced
+ *   "schedule_tc"            scheduling keys on the tensor cores (1, default) or by fp32 SIMT tiles (0)
  *   "dense_passes"           tf32 passes of coral_exact_knn's selection scans: 3 (default) or 1
  *   "schedule"               run large batches grouped by the entry points' neighbour each query is
  *                            closest to, for L2 locality: 0 = automatic for batches >= 8192,
@@ -255,9 +273,50 @@ int coral_build_end(coral_index_t* h);
 int coral_merge_shards(coral_index_t* h, const int32_t* d_ids, const float* d_dists, int G, int Q,
                        int k, int32_t* d_ids_out, float* d_dists_out, void* stream);
 
+/* The same with the G per-shard blocks `shard_stride` elements apart (>= Q*k): merges a
+ * slice of a larger gathered buffer in place.  No counterpart in the reference. */
+int coral_merge_shards_strided(coral_index_t* h, const int32_t* d_ids, const float* d_dists, int G,
+                               int Q, int k, int64_t shard_stride, int32_t* d_ids_out,
+                               float* d_dists_out, void* stream);
+
 /* Maps shard-local result ids to global ids in place through id_map[n_local]
  * (device pointers; ids < 0 stay).  No counterpart in the reference. */
 int coral_map_ids(coral_index_t* h, int32_t* d_ids, int64_t count, const int32_t* d_id_map, void* stream);
+
+/* ---- multi-GPU (no counterpart in the reference, which drives one GPU: src/gpufuncs.cu:35,84;
+ * its tiers for bases beyond one GPU are host memory and SSD, src/index_gpu.cpp:256-257) ----
+ *
+ * One handle per GPU.  An index that fits one GPU is replicated and the batch split: rank r of
+ * `world` searches rows [lo, hi) of the batch (coral_query_slice) with plain coral_search -- no
+ * collective.  An index that does not fit is sharded: every rank holds one shard (own graph,
+ * own entry points, id_map[local] = global id), searches ALL queries, and coral_search_sharded
+ * exchanges the per-shard top-k with ONE ncclAllGather and merges this rank's slice only.
+ * NCCL is loaded with dlopen("libnccl.so.2") at the first coral_comm_* call. */
+typedef struct coral_comm coral_comm_t;
+
+/* 128-byte NCCL unique id for coral_comm_create (make it on one rank, hand it to the others). */
+int coral_comm_unique_id(void* id128);
+/* One communicator per process and GPU (collective: every rank must call it). */
+int coral_comm_create(coral_comm_t** out, int device, int world, int rank, const void* id128);
+/* n communicators for n GPUs driven by ONE process (out: n pointers); ranks = positions. */
+int coral_comm_create_all(coral_comm_t** out, const int* devices, int n);
+int coral_comm_destroy(coral_comm_t* c);
+int coral_comm_world(coral_comm_t* c);
+int coral_comm_rank(coral_comm_t* c);
+const char* coral_comm_last_error(coral_comm_t* c);
+
+/* Rows [*lo, *hi) of a Q-query batch that `rank` of `world` owns (contiguous, balanced). */
+void coral_query_slice(int Q, int world, int rank, int* lo, int* hi);
+
+/* Sharded search, collective over the communicator: the same Q queries (device pointer) on
+ * every rank.  Local search (as coral_search_async) -> global ids through d_id_map (device,
+ * NULL = ids are global already) -> one ncclAllGather of ids and distances in a single buffer
+ * -> merge by (distance, id) of THIS rank's slice of the batch (coral_query_slice): ids_out /
+ * dists_out (nullable) receive (hi - lo) * k entries, host or device pointers.  Everything is
+ * enqueued on `stream`; the call synchronises only when it has to copy to host buffers.
+ * Communication buffers are grown on demand and kept.  world * k <= 4096. */
+int coral_search_sharded(coral_index_t* h, coral_comm_t* c, const int32_t* d_id_map, const float* d_queries,
+                         int Q, int L, int k, int32_t* ids_out, float* dists_out, void* stream);
 
 /* The beam search for callers that cannot allocate device memory at search time
  * (a server whose pool already owns the GPU, a plugin inside another framework's

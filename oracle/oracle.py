@@ -243,9 +243,10 @@ def build_graph(base, train_knn, metric, max_degree, batch=1024, ce=True, ce_L=2
         iso = np.nonzero(st.deg == 0)[0].astype(np.int32)
         if log:
             log(f"oracle build: {len(iso)} isolated nodes after NAP")
+        first_connected = int(np.nonzero(st.deg > 0)[0][0])
         for s in range(0, len(iso), ce_search_batch):
             chunk = iso[s:s + ce_search_batch]
-            start = select_start_ids(st.adj, int(np.nonzero(st.deg > 0)[0][0]), n_start)
+            start = select_start_ids(st.adj, first_connected, n_start)
             ids, dists, _ = search(base, st.adj, start, base[chunk], ce_L, kb, metric)
             for j in range(0, len(chunk), ce_nap_batch):
                 ce_batch(base, st, chunk[j:j + ce_nap_batch], ids[j:j + ce_nap_batch], dists[j:j + ce_nap_batch], metric)

@@ -28,14 +28,20 @@ class Case:
 
 @functools.lru_cache(maxsize=None)
 def structured(metric: str, n: int = 12000, dim: int | None = None, deg: int = 32, nq: int = 96) -> Case:
-    """A CORAL-shaped graph on clustered cross-modal data."""
+    """A CORAL graph -- the reference's build (exact lists -> NAP -> CE), run by its CPU restatement --
+    on clustered cross-modal data with overlapping clusters."""
+    from oracle import oracle
     if metric == "l2":
-        ds = synth.make_l2_mixture(n, n // 8, nq, dim=dim or 200, centers=max(2, n // 1000), seed=11)
+        d = dim or 200
+        ds = synth.make_l2_mixture(n, n // 4, nq, dim=d, centers=max(2, n // 1000), seed=11, rot_dims=min(60, d),
+                                   latent_dim=8, latent_jitter=0.5)
     else:
-        ds = synth.make_ip_cones(n, n // 8, nq, dim=dim or 512, clusters=max(2, n // 1500), seed=12)
-    g = synth.build_graph(ds.base, ds.train, ds.metric, max_degree=deg, k_b=50, seed=13)
-    return Case(f"structured_{metric}_{n}x{ds.base.shape[1]}_d{deg}", ds.base.numpy(), g.adj.numpy(),
-                g.start_ids.numpy(), ds.test.numpy(), metric, deg)
+        ds = synth.make_ip_cones(n, n // 4, nq, dim=dim or 512, clusters=max(2, n // 1500), seed=12, latent_dim=8,
+                                 latent_jitter=0.5)
+    base = ds.base.numpy()
+    knn, _ = oracle.exact_knn(base, ds.train.numpy(), 50, metric)
+    st, start = oracle.build_graph(base, knn, metric, deg, batch=512, ce_L=128, ce_search_batch=4096, ce_nap_batch=1024)
+    return Case(f"structured_{metric}_{n}x{base.shape[1]}_d{deg}", base, st.adj, start, ds.test.numpy(), metric, deg)
 
 
 @functools.lru_cache(maxsize=None)

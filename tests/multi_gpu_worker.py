@@ -48,13 +48,19 @@ def main():
         ix.set_adjacency(adj_r)
         ix.set_start_ids(start_r)
         ix.prepare(len(c.queries), L, k)
-        sh = sharded.ShardedIndex(ix, torch.from_numpy(ids_r).cuda())
-        m_ids, m_d = sh.search(dq, L, k)
+        comm = sharded.Communicator.from_torch(local)
+        sh = sharded.ShardedIndex(ix, torch.from_numpy(ids_r).cuda(), comm)
+        torch.cuda.synchronize()
+        m_ids, m_d, s_lo, s_hi = sh.search(dq, L, k)          # this rank's slice of the merged batch
+        torch.cuda.synchronize()
+        ix.check()
         m_ids, m_d = m_ids.cpu().numpy(), m_d.cpu().numpy()
+        assert (s_lo, s_hi) == sharded.query_slice(len(c.queries), world, rank)
+        comm.close()
     per = [oracle.search(b, a, s, c.queries, L, k, c.metric) for (_, b, a, s) in shards]
     g_ids = np.stack([np.where(p[0] >= 0, shards[r][0][np.maximum(p[0], 0)], -1) for r, p in enumerate(per)])
     o_ids, o_d = oracle.merge_shards(g_ids, np.stack([p[1] for p in per]), c.metric)
-    assert np.array_equal(m_ids, o_ids) and np.array_equal(m_d.view(np.uint32), o_d.view(np.uint32))
+    assert np.array_equal(m_ids, o_ids[s_lo:s_hi]) and np.array_equal(m_d.view(np.uint32), o_d[s_lo:s_hi].view(np.uint32))
     dist.barrier()
     if rank == 0:
         print("MULTI_GPU_OK world=%d" % world)

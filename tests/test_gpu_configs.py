@@ -18,20 +18,18 @@ def _np(x):
     return x.cpu().numpy() if hasattr(x, "cpu") else np.asarray(x)
 
 
-def _build(metric, n, dim, deg, groups, nq, seed=20260001, draw_seed=None):
+def _build(config, n=None, nq=10_000, draw_seed=None):
+    """Synthetic data of a benchmark configuration and its graph, built by the library on this GPU."""
     import torch
     from coral_b200 import capi, synth
-    if metric == "ip":
-        ds = synth.make_ip_cones(n, 100_000, nq, dim=dim, clusters=groups, seed=seed, device="cuda", draw_seed=draw_seed)
-    else:
-        ds = synth.make_l2_mixture(n, 100_000, nq, dim=dim, centers=groups, seed=seed, device="cuda", draw_seed=draw_seed)
-    g = synth.build_graph(ds.base, ds.train, ds.metric, max_degree=deg, k_b=100, cell_size=512)
+    c = synth.CONFIGS[config]
+    ds = synth.make_config(config, 100_000, nq, n=n, device="cuda", draw_seed=draw_seed)
+    ix = capi.Index(ds.base.shape[0], c["dim"], c["deg"], c["kind"])
+    ix.attach_vectors(ds.base)
+    ix.build(ds.train, kb=100)
     ds.train = None
     torch.cuda.empty_cache()
-    ix = capi.Index(n, dim, deg, metric)
-    ix.attach_vectors(ds.base)
-    ix.set_adjacency(g.adj)
-    ix.set_start_ids(g.start_ids)
+    g = synth.Graph(ix.get_adjacency_tensor("cuda"), torch.from_numpy(ix.get_start_ids()), c["deg"])
     return ds, g, ix
 
 
@@ -56,14 +54,14 @@ def _check_all(ix, ds, g, metric, Ls, ks, rows=None):
 
 
 def test_config1_every_query_every_L_both_k():
-    ds, g, ix = _build("l2", 1_000_000, 200, 32, 1000, 10_000)
+    ds, g, ix = _build("c1")
     with ix:
         ix.prepare(10_000, 512, 100)
         _check_all(ix, ds, g, "l2", [64, 128, 256, 512], [10, 100])
 
 
 def test_config2_every_query_every_L():
-    ds, g, ix = _build("ip", 1_000_000, 512, 32, 410, 10_000)
+    ds, g, ix = _build("c2")
     with ix:
         ix.prepare(10_000, 256, 10)
         _check_all(ix, ds, g, "ip", [64, 128, 256], [10])
@@ -73,7 +71,7 @@ def test_config4_one_full_size_shard_k100():
     import torch
     if torch.cuda.mem_get_info()[1] < 100e9:
         pytest.skip("needs a GPU with the shard's memory")
-    ds, g, ix = _build("l2", 12_500_000, 200, 32, 10_000, 100_000, draw_seed=20261001)
+    ds, g, ix = _build("c4", nq=100_000, draw_seed=20261001)
     with ix:
         ix.prepare(100_000, 256, 100)
         rows = np.arange(0, 100_000, 100_000 // 256)[:256]
@@ -89,7 +87,7 @@ def test_config4_merge_of_two_shards_equals_the_oracle_merge():
     per_shard, handles = [], []
     try:
         for r in range(G):
-            ds, g, ix = _build("l2", n_local, 200, 32, 500, nq, draw_seed=20261001 + r)
+            ds, g, ix = _build("c4", n=n_local, nq=nq, draw_seed=20261001 + r)
             handles.append(ix)
             ix.prepare(nq, L, k)
             ids, d, st, _ = ix.search(ds.test, L, k, dists=True, stats=True)

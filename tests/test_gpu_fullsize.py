@@ -1,11 +1,14 @@
 """The search at the full size of the headline workload (10M x 512 inner product, degree 64,
 100 000 queries, L = 64, k = 10) on seeded synthetic inputs of that shape.
 
-The oracle cannot search 100 000 queries on 10M points in test time, so this file checks what does
-not depend on size: order and uniqueness of every result row, returned distances recomputed bit for
-bit, the same bits from a second call, from the unscheduled order and from the small-batch
-(cluster) mode, recall against exact search -- and full oracle parity (ids, distance bits,
-counters) on a handful of the queries.
+The graph is built here by the library (tensor-core k-NN lists of 100 000 training queries ->
+neighbourhood-aware projection -> connectivity enhancement), as the reference builds it.  The oracle
+cannot search 100 000 queries on 10M points in test time, so this file checks what does not depend
+on size: order and uniqueness of every result row, returned distances recomputed bit for bit, the
+same bits from a second call, from the unscheduled order and from the small-batch (cluster) mode,
+recall against exact search -- and full oracle parity (ids, distance bits, counters) on a
+thousand queries at every configured beam capacity and on the small-batch sizes, with and
+without deleted points.
 """
 import numpy as np
 import pytest
@@ -23,12 +26,13 @@ def full():
     from coral_b200 import capi, synth
     if torch.cuda.mem_get_info()[1] < 100e9:
         pytest.skip("needs a GPU with the headline workload's memory")
-    ds = synth.make_ip_cones(N, 100_000, Q, dim=DIM, clusters=4096, seed=1, device="cuda")
-    g = synth.build_graph(ds.base, ds.train, ds.metric, max_degree=DEG, k_b=100, cell_size=512)
+    ds = synth.make_config("c3", 100_000, Q, seed=1, device="cuda")
     ix = capi.Index(N, DIM, DEG, "ip")
     ix.attach_vectors(ds.base)
-    ix.set_adjacency(g.adj)
-    ix.set_start_ids(g.start_ids)
+    ix.build(ds.train, kb=100)            # the reference's build (k-NN lists -> NAP -> CE) on this GPU
+    ds.train = None
+    torch.cuda.empty_cache()
+    g = synth.Graph(ix.get_adjacency_tensor("cuda"), torch.from_numpy(ix.get_start_ids()), DEG)
     ix.prepare(Q, 256, K)
     ids, d, st, hops = ix.search(ds.test, L, K, dists=True, stats=True)
     to_np = lambda x: x.cpu().numpy() if hasattr(x, "cpu") else np.asarray(x)
@@ -85,7 +89,7 @@ def test_same_bits_again_unscheduled_and_in_small_batches(full):
 def test_recall_against_exact_search(full):
     synth, ds = full["synth"], full["ds"]
     n_gt = 1000
-    gt = synth.exact_knn(ds.base, ds.test[:n_gt], K, "ip").cpu().numpy()
+    gt = full["to_np"](full["ix"].exact_knn(ds.test[:n_gt], K, dists=False)[0])
     hit = sum(len(set(a) & set(b)) for a, b in zip(full["ids"][:n_gt], gt))
     assert hit / (K * n_gt) >= 0.95
 

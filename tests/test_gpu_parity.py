@@ -281,3 +281,61 @@ def test_committed_fixture():
         assert np.array_equal(ids, z[f"{tag}_ids"])
         assert np.array_equal(d.view(np.uint32), z[f"{tag}_dists"].view(np.uint32))
         assert np.array_equal(st[:, :7], z[f"{tag}_stats"][:, :7])
+
+
+def test_sharded_entry_point_on_one_rank_equals_search_plus_id_map():
+    """coral_search_sharded with a one-rank communicator: local search, id mapping, the NCCL
+    all-gather (a copy at world 1) and the slice merge must reproduce coral_search's rows with
+    the ids sent through the id map."""
+    import torch
+    from coral_b200 import sharded
+    c = cases.structured("ip")
+    rng = np.random.default_rng(4)
+    id_map = rng.permutation(10 * c.n)[:c.n].astype(np.int32)        # any injective local -> global map
+    with make_index(c, len(c.queries), 128, 100) as ix:
+        comm = sharded.Communicator.from_torch(0)
+        sh = sharded.ShardedIndex(ix, torch.from_numpy(id_map).cuda(), comm)
+        dq = torch.from_numpy(c.queries).cuda()
+        for L, k in [(64, 10), (128, 100)]:
+            want_ids, want_d, _, _ = ix.search(c.queries, L, k)
+            torch.cuda.synchronize()
+            ids, d, lo, hi = sh.search(dq, L, k)
+            torch.cuda.synchronize()
+            ix.check()
+            assert (lo, hi) == (0, len(c.queries))
+            assert np.array_equal(ids.cpu().numpy(), id_map[want_ids])
+            assert np.array_equal(d.cpu().numpy().view(np.uint32), want_d.view(np.uint32))
+        comm.close()
+
+
+@pytest.mark.parametrize("metric", ["l2", "ip"])
+def test_tensor_core_scheduling_keys_and_the_deterministic_order(metric):
+    """The pre-pass that orders large batches: keys from the tcgen05 dense scan (exact nearest
+    frontier row after the re-rank) or from the fp32 SIMT tiles; either way the order is a
+    permutation, the same on every call, and results stay at their own rows."""
+    import torch
+    c = cases.structured(metric)
+    reps = np.concatenate([c.queries] * 50)[:4500]          # > 4096 queries: the tensor-core path is set up
+    ref_ids, ref_d, ref_st = oracle.search(c.base, c.adj, c.start, c.queries, 64, 10, c.metric)
+    orders = {}
+    for tc in (1, 0):
+        with make_index(c, len(reps), 64, 10, options={"schedule": 1, "schedule_tc": tc}) as ix:
+            ids, d, st, _ = ix.search(reps, 64, 10, stats=True)
+            assert ix.get_option("last_scheduled") == 1
+            for r in range(0, len(reps), len(c.queries)):
+                m = min(len(c.queries), len(reps) - r)
+                assert np.array_equal(ids[r:r + m], ref_ids[:m]) and np.array_equal(st[r:r + m, :7], ref_st[:m, :7])
+            dq = torch.from_numpy(reps).cuda()
+            o1 = ix.query_order(dq)
+            o2 = ix.query_order(dq)
+            torch.cuda.synchronize()
+            o1, o2 = o1.cpu().numpy(), o2.cpu().numpy()
+            assert np.array_equal(o1, o2)                                   # deterministic
+            assert np.array_equal(np.sort(o1), np.arange(len(reps)))        # a permutation
+            orders[tc] = o1
+    # identical queries share a key, so they keep their row order (the sort is stable) in both variants
+    for o in orders.values():
+        pos = np.empty(len(reps), np.int64)
+        pos[o] = np.arange(len(reps))
+        copies = np.arange(7, len(reps), len(c.queries))                  # the copies of query 7
+        assert np.array_equal(np.sort(pos[copies]), pos[copies])
