@@ -22,13 +22,14 @@ EXPORTS = (
     "coral_version", "coral_compiled_sm", "coral_plan", "coral_index_create", "coral_index_destroy",
     "coral_index_set_vectors", "coral_index_attach_vectors", "coral_index_set_slots",
     "coral_index_set_adjacency", "coral_index_set_start_ids", "coral_index_select_start_ids",
-    "coral_index_get_adjacency", "coral_index_get_start_ids",
+    "coral_index_get_adjacency", "coral_index_get_start_ids", "coral_index_stream",
     "coral_index_set_deleted",
     "coral_search_prepare", "coral_search_free", "coral_search", "coral_search_async",
     "coral_search_check", "coral_query_order", "coral_last_kernel_ms", "coral_last_total_ms", "coral_launch_count",
     "coral_set_option", "coral_get_option", "coral_count_hits", "coral_exact_knn", "coral_last_dense_ms",
     "coral_last_dense_flops", "coral_build_begin", "coral_build_nap", "coral_build_connect_enhance",
-    "coral_build_get_graph", "coral_build_set_graph", "coral_build_end", "coral_merge_shards",
+    "coral_build_get_graph", "coral_build_set_graph", "coral_build_end", "coral_index_set_live",
+    "coral_build_begin_from_graph", "coral_delete", "coral_insert", "coral_merge_shards",
     "coral_merge_shards_strided", "coral_comm_unique_id", "coral_comm_create", "coral_comm_create_all",
     "coral_comm_destroy", "coral_comm_world", "coral_comm_rank", "coral_comm_last_error", "coral_query_slice",
     "coral_search_sharded",
@@ -68,6 +69,7 @@ def load():
         "coral_index_set_adjacency": (C.c_int, [vp, i32p, C.c_int]),
         "coral_index_set_start_ids": (C.c_int, [vp, i32p, C.c_int]),
         "coral_index_select_start_ids": (C.c_int, [vp, C.c_int, C.c_int, i32p]),
+        "coral_index_stream": (vp, [vp]),
         "coral_index_get_adjacency": (C.c_int, [vp, i32p]),
         "coral_index_get_start_ids": (C.c_int, [vp, i32p, C.c_int]),
         "coral_index_set_deleted": (C.c_int, [vp, vp]),
@@ -92,6 +94,10 @@ def load():
         "coral_build_get_graph": (C.c_int, [vp, i32p, f32p, i32p]),
         "coral_build_set_graph": (C.c_int, [vp, i32p, f32p, i32p]),
         "coral_build_end": (C.c_int, [vp]),
+        "coral_index_set_live": (C.c_int, [vp, C.c_int64]),
+        "coral_build_begin_from_graph": (C.c_int, [vp]),
+        "coral_delete": (C.c_int, [vp, i32p, C.c_int, C.c_int]),
+        "coral_insert": (C.c_int, [vp, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
         "coral_merge_shards": (C.c_int, [vp, i32p, f32p, C.c_int, C.c_int, C.c_int, i32p, f32p, vp]),
         "coral_map_ids": (C.c_int, [vp, i32p, C.c_int64, i32p, vp]),
         "coral_merge_shards_strided": (C.c_int, [vp, i32p, f32p, C.c_int, C.c_int, C.c_int, C.c_int64, i32p, f32p, vp]),
@@ -381,6 +387,19 @@ class Index:
 
     def build_end(self):
         self._check(self._lib.coral_build_end(self._h))
+
+    def set_live(self, live: int):
+        self._check(self._lib.coral_index_set_live(self._h, int(live)))
+
+    def update_begin(self):
+        self._check(self._lib.coral_build_begin_from_graph(self._h))
+
+    def delete(self, ids, M: int = 0):
+        a = np.ascontiguousarray(ids, dtype=np.int32)
+        self._check(self._lib.coral_delete(self._h, C.c_void_p(a.ctypes.data), int(a.size), int(M)))
+
+    def insert(self, first_id: int, count: int, kb: int, L: int = 0, batch: int = 0, M: int = 0):
+        self._check(self._lib.coral_insert(self._h, int(first_id), int(count), int(kb), int(L), int(batch), int(M)))
 
     def build(self, train_queries, kb: int = 100, batch: int = 0, ce: bool = True, ce_L: int = 0,
               ce_search_batch: int = 0, ce_nap_batch: int = 0, M: int = 0):

@@ -188,6 +188,26 @@ __device__ void warp_prune(PruneScratch& S, int n_cand, int max_degree, int metr
     }
 }
 
+// src/update.cu:530-577 (the update path's fill): every kept candidate in order, THEN pruned ones
+// while the row has room.  Lane 0 only.
+__device__ int fill_row_kept_first(const PruneScratch& S, int n_cand, int max_degree, int metric, int32_t* nbrs,
+                                   float* dists) {
+    int nbr_num = 0;
+    for (int pass = 0; pass < 2; ++pass) {
+        const uint8_t want = pass == 0 ? S_RETAINED : S_DISCARDED;
+        for (int j = 0; j < n_cand && nbr_num < max_degree; ++j) {
+            const uint8_t st = S.status[j];
+            if (st == S_INVALID) break;
+            if (st == want) {
+                nbrs[nbr_num] = S.id_by_col[(int)(uint32_t)(S.keys[j] & 0xffffffffu)];
+                dists[nbr_num] = dist_of((uint32_t)(S.keys[j] >> 32), metric);
+                ++nbr_num;
+            }
+        }
+    }
+    return nbr_num;
+}
+
 // src/upd_gpu.cu:106-135: kept first, then pruned ones while the row has room.  Lane 0 only.
 __device__ int fill_row(const PruneScratch& S, int n_cand, int max_degree, int metric, int32_t* nbrs, float* dists) {
     int retained = 0;
@@ -307,7 +327,7 @@ __global__ void __launch_bounds__(128) ce_reverse_kernel(const float* __restrict
                                                          const int32_t* __restrict__ iso_ids, int n_iso,
                                                          const int32_t* __restrict__ res_ids,
                                                          const float* __restrict__ res_dists, int kb, int64_t n,
-                                                         const uint32_t* __restrict__ claim) {
+                                                         const uint32_t* __restrict__ claim, int mode) {
     __shared__ uint8_t flags[4][128];   // bit 0: stored neighbour closer to the node than the isolated node is
                                         // bit 1: ... and closer to the isolated node than the node is (occludes it)
                                         // bit 2: the isolated node occludes the stored neighbour
@@ -317,8 +337,9 @@ __global__ void __launch_bounds__(128) ce_reverse_kernel(const float* __restrict
     const int knn_id = res_ids[e];
     if (knn_id < 0 || (int64_t)knn_id >= n || claim[knn_id] != (uint32_t)e) return;
     const int iso_id = iso_ids[e / kb];
-    const float knn_dist = res_dists[e];
     const float* iso_vec = vecs + (size_t)iso_id * dim;
+    // insert path (src/update.cu:139): the candidate's distance is recomputed, not taken from the search
+    const float knn_dist = (mode & 1) ? dist_seq(iso_vec, vecs + (size_t)knn_id * dim, dim, metric) : res_dists[e];
     int32_t* nb = adj + (size_t)knn_id * deg_pad;
     float* ds = ndist + (size_t)knn_id * deg_pad;
     const int d = deg[knn_id];
@@ -366,7 +387,7 @@ __global__ void __launch_bounds__(128) ce_prune_kernel(const float* __restrict__
                                                        const int32_t* __restrict__ iso_ids, int n_iso,
                                                        const int32_t* __restrict__ res_ids,
                                                        const float* __restrict__ res_dists, int kb, int64_t n,
-                                                       uint32_t* __restrict__ claim) {
+                                                       uint32_t* __restrict__ claim, int mode) {
     __shared__ PruneScratch scratch[4];
     __shared__ int32_t row_n[4][128];
     __shared__ float row_d[4][128];
@@ -380,7 +401,9 @@ __global__ void __launch_bounds__(128) ce_prune_kernel(const float* __restrict__
         if (col < kb) {
             id = res_ids[(size_t)i * kb + col];
             if (id >= 0 && (int64_t)id < n) {
-                key = ((uint64_t)ord_of(res_dists[(size_t)i * kb + col], metric) << 32) | (uint32_t)col;
+                const float dc = (mode & 1) ? dist_seq(vecs + (size_t)iso_ids[i] * dim, vecs + (size_t)id * dim, dim, metric)
+                                            : res_dists[(size_t)i * kb + col];
+                key = ((uint64_t)ord_of(dc, metric) << 32) | (uint32_t)col;
                 claim[id] = kUnclaimed;     // the reverse edges of this batch are in place: free the claim
             } else {
                 id = -1;
@@ -397,7 +420,9 @@ __global__ void __launch_bounds__(128) ce_prune_kernel(const float* __restrict__
         return dist_seq(vecs + (size_t)id_i * dim, vecs + (size_t)id_j * dim, dim, metric);
     });
     int nd = 0;
-    if (lane == 0) nd = fill_row(S, kb, max_degree, metric, row_n[warp], row_d[warp]);
+    if (lane == 0)
+        nd = (mode & 2) ? fill_row_kept_first(S, kb, max_degree, metric, row_n[warp], row_d[warp])
+                        : fill_row(S, kb, max_degree, metric, row_n[warp], row_d[warp]);
     nd = __shfl_sync(0xffffffffu, nd, 0);
     const int id = iso_ids[i];
     for (int j = lane; j < deg_pad; j += 32) {
@@ -405,6 +430,181 @@ __global__ void __launch_bounds__(128) ce_prune_kernel(const float* __restrict__
         ndist[(size_t)id * deg_pad + j] = j < nd ? row_d[warp][j] : 0.f;
     }
     if (lane == 0) deg[id] = nd;
+}
+
+// ------------------------------------------------------------------------------------- update
+
+// Distances of the stored edges and the degrees of a graph given as adjacency only.
+__global__ void edge_dist_kernel(const float* __restrict__ vecs, int dim, int metric, const int32_t* __restrict__ adj,
+                                 int deg_pad, int64_t n, float* __restrict__ ndist, int32_t* __restrict__ deg) {
+    const int lane = threadIdx.x & 31;
+    const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < n; i += warps) {
+        int cnt = 0;
+        for (int j = lane; j < deg_pad; j += 32) {
+            const int id = adj[(size_t)i * deg_pad + j];
+            const bool ok = id >= 0 && (int64_t)id < n;
+            ndist[(size_t)i * deg_pad + j] = ok ? dist_seq(vecs + (size_t)i * dim, vecs + (size_t)id * dim, dim, metric) : 0.f;
+            cnt += __popc(__ballot_sync(0xffffffffu, ok));
+        }
+        if (lane == 0) deg[i] = cnt;
+    }
+}
+
+__global__ void mark_deleted_kernel(const int32_t* __restrict__ ids, int count, int64_t n, uint32_t* __restrict__ bits,
+                                    int32_t* __restrict__ pos_of) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x) {
+        const int id = ids[i];
+        if (id < 0 || (int64_t)id >= n) continue;
+        atomicOr(bits + (id >> 5), 1u << (id & 31));
+        pos_of[id] = i;
+    }
+}
+
+// In-neighbours of the deleted nodes: first pass counts, second pass fills (fill != nullptr).
+__global__ void innbr_scan_kernel(const int32_t* __restrict__ adj, const int32_t* __restrict__ deg, int deg_pad, int64_t n,
+                                  const uint32_t* __restrict__ bits, const int32_t* __restrict__ pos_of,
+                                  int* __restrict__ counts, const int* __restrict__ offsets, int32_t* __restrict__ fill) {
+    const long long total = n * (long long)deg_pad;
+    for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+        const long long i = t / deg_pad;
+        const int j = (int)(t - i * deg_pad);
+        if (j >= deg[i] || ((bits[i >> 5] >> (i & 31)) & 1u)) continue;       // deleted rows are not repaired
+        const int id = adj[t];
+        if (id < 0 || (int64_t)id >= n || !((bits[id >> 5] >> (id & 31)) & 1u)) continue;
+        const int p = pos_of[id];
+        if (p < 0) continue;                                                     // deleted by an earlier call: no longer anyone's neighbour
+        const int slot = atomicAdd(&counts[p], 1);
+        if (fill) fill[offsets[p] + slot] = (int32_t)i;
+    }
+}
+
+// Ascending order inside every list (the fill order is arbitrary): one CTA per list, bitonic sort in
+// shared memory in pieces of 4096 followed by a merge through global memory when a list is longer.
+__global__ void __launch_bounds__(256) sort_lists_kernel(int32_t* __restrict__ lists, const int* __restrict__ offsets,
+                                                         int n_lists, int32_t* __restrict__ piv_del,
+                                                         const int32_t* __restrict__ del_ids) {
+    __shared__ int32_t s[4096];
+    for (int l = blockIdx.x; l < n_lists; l += gridDim.x) {
+        const int lo = offsets[l], hi = offsets[l + 1], len = hi - lo;
+        for (int i = threadIdx.x; i < len; i += 256) piv_del[lo + i] = del_ids[l];
+        if (len <= 1) continue;
+        if (len <= 4096) {
+            int n2 = 2;
+            while (n2 < len) n2 <<= 1;
+            for (int i = threadIdx.x; i < n2; i += 256) s[i] = i < len ? lists[lo + i] : 0x7fffffff;
+            __syncthreads();
+            for (int k = 2; k <= n2; k <<= 1)
+                for (int j = k >> 1; j > 0; j >>= 1) {
+                    for (int i = threadIdx.x; i < n2; i += 256) {
+                        const int ixj = i ^ j;
+                        if (ixj > i) {
+                            const int32_t a = s[i], b = s[ixj];
+                            if ((a > b) == ((i & k) == 0)) {
+                                s[i] = b;
+                                s[ixj] = a;
+                            }
+                        }
+                    }
+                    __syncthreads();
+                }
+            for (int i = threadIdx.x; i < len; i += 256) lists[lo + i] = s[i];
+            __syncthreads();
+        } else if (threadIdx.x == 0) {
+            // a hub with more than 4096 in-neighbours: heap sort in place by one thread (rare)
+            int32_t* a = lists + lo;
+            for (int start = len / 2 - 1; start >= 0; --start) {
+                int root = start;
+                for (;;) {
+                    int child = 2 * root + 1;
+                    if (child >= len) break;
+                    if (child + 1 < len && a[child] < a[child + 1]) ++child;
+                    if (a[root] >= a[child]) break;
+                    const int32_t t = a[root]; a[root] = a[child]; a[child] = t;
+                    root = child;
+                }
+            }
+            for (int end = len - 1; end > 0; --end) {
+                const int32_t t0 = a[0]; a[0] = a[end]; a[end] = t0;
+                int root = 0;
+                for (;;) {
+                    int child = 2 * root + 1;
+                    if (child >= end) break;
+                    if (child + 1 < end && a[child] < a[child + 1]) ++child;
+                    if (a[root] >= a[child]) break;
+                    const int32_t t = a[root]; a[root] = a[child]; a[child] = t;
+                    root = child;
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// Repair of one in-neighbour (src/update.cu:312-391, :499-583): one warp per (deleted node,
+// in-neighbour) pair; the first pair of the batch that names an in-neighbour repairs it.
+__global__ void __launch_bounds__(128) delete_prune_kernel(const float* __restrict__ vecs, int dim, int metric,
+                                                           int32_t* __restrict__ adj, float* __restrict__ ndist,
+                                                           int32_t* __restrict__ deg, int deg_pad, int max_degree,
+                                                           const uint32_t* __restrict__ bits,
+                                                           const int32_t* __restrict__ piv_del,
+                                                           const int32_t* __restrict__ piv_in, int n_piv,
+                                                           uint32_t* __restrict__ claim) {
+    __shared__ PruneScratch scratch[4];
+    __shared__ int32_t row_n[4][128];
+    __shared__ float row_d[4][128];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    PruneScratch& S = scratch[warp];
+    const int p = blockIdx.x * 4 + warp;
+    if (p >= n_piv) return;
+    const int I = piv_in[p], D = piv_del[p];
+    if (claim[I] != (uint32_t)p) return;
+    const int deg_i = deg[I], deg_d = deg[D];
+    // candidates in the reference's order: the in-neighbour's surviving neighbours, then the deleted
+    // node's surviving out-neighbours; column = position among the survivors (the stable sort key)
+    int base_col = 0;
+    for (int half = 0; half < 2; ++half) {
+        const int src = half == 0 ? I : D, d = half == 0 ? deg_i : deg_d;
+        for (int b0 = 0; b0 < d; b0 += 32) {
+            const int j = b0 + lane;
+            int id = -1;
+            if (j < d) {
+                id = adj[(size_t)src * deg_pad + j];
+                if (id < 0 || ((bits[id >> 5] >> (id & 31)) & 1u) || (half == 1 && id == I)) id = -1;
+            }
+            const uint32_t m = __ballot_sync(0xffffffffu, id >= 0);
+            if (id >= 0) {
+                const int col = base_col + __popc(m & ((1u << lane) - 1u));
+                const float dc = half == 0 ? ndist[(size_t)I * deg_pad + j]
+                                           : dist_seq(vecs + (size_t)I * dim, vecs + (size_t)id * dim, dim, metric);
+                S.keys[col] = ((uint64_t)ord_of(dc, metric) << 32) | (uint32_t)col;
+                S.id_by_col[col] = id;
+            }
+            base_col += __popc(m);
+        }
+    }
+    for (int col = base_col + lane; col < kCandMax; col += 32) {
+        S.keys[col] = ~0ull;
+        S.id_by_col[col] = -1;
+    }
+    __syncwarp();
+    warp_sort256(S.keys, lane);
+    for (int j = lane; j < kCandMax; j += 32) S.status[j] = S.keys[j] == ~0ull ? S_INVALID : S_INITIAL;
+    __syncwarp();
+    warp_prune(S, 2 * max_degree, max_degree, metric, lane, [&](int, int id_i, int, int id_j) {
+        return dist_seq(vecs + (size_t)id_i * dim, vecs + (size_t)id_j * dim, dim, metric);
+    });
+    int nd = 0;
+    if (lane == 0) nd = fill_row_kept_first(S, 2 * max_degree, max_degree, metric, row_n[warp], row_d[warp]);
+    nd = __shfl_sync(0xffffffffu, nd, 0);
+    for (int j = lane; j < deg_pad; j += 32) {
+        adj[(size_t)I * deg_pad + j] = j < nd ? row_n[warp][j] : -1;
+        ndist[(size_t)I * deg_pad + j] = j < nd ? row_d[warp][j] : 0.f;
+    }
+    if (lane == 0) {
+        deg[I] = nd;
+        claim[I] = kUnclaimed;
+    }
 }
 
 int grid_for(long long items, int per_block, int cap) {
@@ -444,16 +644,51 @@ cudaError_t nap_batch(const BuildGraph& g, const int32_t* d_lists, int B, int kb
 }
 
 cudaError_t ce_batch(const BuildGraph& g, const int32_t* d_iso_ids, int n_iso, const int32_t* d_res_ids,
-                     const float* d_res_dists, int kb, cudaStream_t st, int64_t* launches) {
+                     const float* d_res_dists, int kb, cudaStream_t st, int64_t* launches, int mode) {
     if (kb < 1 || kb > 128 || g.max_degree > 128) return cudaErrorInvalidValue;
     const long long entries = (long long)n_iso * kb;
     claim_kernel<<<grid_for(entries, 256, 2048), 256, 0, st>>>(d_res_ids, entries, g.n, g.claim);
     ce_reverse_kernel<<<(unsigned)((entries + 3) / 4), 128, 0, st>>>(g.vecs, g.dim, g.metric, g.adj, g.ndist, g.deg, g.deg_pad,
                                                                      g.max_degree, d_iso_ids, n_iso, d_res_ids, d_res_dists,
-                                                                     kb, g.n, g.claim);
+                                                                     kb, g.n, g.claim, mode);
     ce_prune_kernel<<<(unsigned)((n_iso + 3) / 4), 128, 0, st>>>(g.vecs, g.dim, g.metric, g.adj, g.ndist, g.deg, g.deg_pad,
                                                                  g.max_degree, d_iso_ids, n_iso, d_res_ids, d_res_dists, kb,
-                                                                 g.n, g.claim);
+                                                                 g.n, g.claim, mode);
+    if (launches) *launches += 3;
+    return cudaGetLastError();
+}
+
+cudaError_t edge_dists(const BuildGraph& g, cudaStream_t st) {
+    edge_dist_kernel<<<grid_for(g.n * 32, 256, 8192), 256, 0, st>>>(g.vecs, g.dim, g.metric, g.adj, g.deg_pad, g.n, g.ndist,
+                                                                     g.deg);
+    return cudaGetLastError();
+}
+
+cudaError_t mark_deleted(const int32_t* d_ids, int count, int64_t n, uint32_t* bits, int32_t* pos_of, cudaStream_t st) {
+    mark_deleted_kernel<<<grid_for(count, 256, 2048), 256, 0, st>>>(d_ids, count, n, bits, pos_of);
+    return cudaGetLastError();
+}
+
+cudaError_t innbr_scan(const BuildGraph& g, const uint32_t* bits, const int32_t* pos_of, int* counts, const int* offsets,
+                       int32_t* fill, cudaStream_t st) {
+    innbr_scan_kernel<<<grid_for(g.n * (long long)g.deg_pad, 256, 16384), 256, 0, st>>>(g.adj, g.deg, g.deg_pad, g.n, bits,
+                                                                                        pos_of, counts, offsets, fill);
+    return cudaGetLastError();
+}
+
+cudaError_t sort_innbr_lists(int32_t* lists, const int* offsets, int n_lists, int32_t* piv_del, const int32_t* d_del_ids,
+                             cudaStream_t st) {
+    sort_lists_kernel<<<grid_for(n_lists, 1, 8192), 256, 0, st>>>(lists, offsets, n_lists, piv_del, d_del_ids);
+    return cudaGetLastError();
+}
+
+cudaError_t delete_batch(const BuildGraph& g, const uint32_t* bits, const int32_t* piv_del, const int32_t* piv_in, int n_piv,
+                         cudaStream_t st, int64_t* launches) {
+    if (g.max_degree > 64) return cudaErrorInvalidValue;
+    claim_kernel<<<grid_for(n_piv, 256, 2048), 256, 0, st>>>(piv_in, n_piv, g.n, g.claim);
+    delete_prune_kernel<<<(unsigned)((n_piv + 3) / 4), 128, 0, st>>>(g.vecs, g.dim, g.metric, g.adj, g.ndist, g.deg, g.deg_pad,
+                                                                     g.max_degree, bits, piv_del, piv_in, n_piv, g.claim);
+    unclaim_kernel<<<grid_for(n_piv, 256, 2048), 256, 0, st>>>(piv_in, n_piv, g.n, g.claim);
     if (launches) *launches += 3;
     return cudaGetLastError();
 }

@@ -62,6 +62,7 @@ struct coral_index {
     int sm_count = 0;
     int smem_optin = 0;
     int64_t n = 0;
+    int64_t live_n = 0;   // rows [0, live_n) are part of the index; the rest wait to be inserted
     int dim = 0, max_degree = 0, deg_pad = 0, metric = 0;
     cudaStream_t stream = nullptr;
     cudaEvent_t ev_t0 = nullptr, ev_k0 = nullptr, ev_k1 = nullptr, ev_t1 = nullptr;
@@ -373,6 +374,7 @@ int coral_index_create(coral_index_t** out, int device, int64_t n, int dim, int 
     h->sm_count = prop.multiProcessorCount;
     h->smem_optin = (int)prop.sharedMemPerBlockOptin;
     h->n = n;
+    h->live_n = n;
     h->dim = dim;
     h->max_degree = max_degree;
     h->deg_pad = max_degree <= 32 ? 32 : (max_degree <= 64 ? 64 : 128);
@@ -497,6 +499,8 @@ int coral_index_set_start_ids(coral_index_t* h, const int32_t* ids, int M) {
     h->frontier_dirty = true;
     return CORAL_OK;
 }
+
+void* coral_index_stream(coral_index_t* h) { return h ? (void*)h->stream : nullptr; }
 
 int coral_index_get_adjacency(coral_index_t* h, int32_t* adj_out) {
     if (!h || !adj_out) return fail(h, CORAL_ERR_ARG, "null argument");
@@ -1036,7 +1040,7 @@ int coral_exact_knn(coral_index_t* h, const float* queries, int Q, int k, int32_
     if (!h || Q < 0 || (Q > 0 && (!queries || !ids_out))) return fail(h, CORAL_ERR_ARG, "null argument");
     if (!h->d_vecs) return fail(h, CORAL_ERR_STATE, "exact knn: no vectors set");
     if (int rc = ensure_device(h)) return rc;
-    return exact_knn_over(h, h->d_vecs, h->n, queries, Q, k, h->opt.dense_passes == 1 ? 1 : 3, ids_out, dists_out,
+    return exact_knn_over(h, h->d_vecs, h->live_n, queries, Q, k, h->opt.dense_passes == 1 ? 1 : 3, ids_out, dists_out,
                           uncertified_out);
 }
 
@@ -1154,7 +1158,7 @@ int coral_build_connect_enhance(coral_index_t* h, int kb, int L, int search_batc
     CK(cudaMemcpy(degs.data(), h->d_deg, degs.size() * sizeof(int32_t), cudaMemcpyDeviceToHost));
     std::vector<int32_t> iso;                                         // src/enhance.cu:582-607, ascending ids
     int first_connected = -1;
-    for (int64_t i = 0; i < h->n; ++i) {
+    for (int64_t i = 0; i < h->live_n; ++i) {
         if (degs[(size_t)i] == 0) iso.push_back((int32_t)i);
         else if (first_connected < 0) first_connected = (int)i;
     }
@@ -1203,6 +1207,177 @@ int coral_build_connect_enhance(coral_index_t* h, int kb, int L, int search_batc
     if (e != cudaSuccess) {
         cudaGetLastError();
         return fail(h, CORAL_ERR_CUDA, std::string("build: ") + cudaGetErrorString(e));
+    }
+    return rc;
+}
+
+int coral_index_set_live(coral_index_t* h, int64_t live) {
+    if (!h || live < 1 || live > h->n) return fail(h, CORAL_ERR_ARG, "live count must be in [1, n]");
+    h->live_n = live;
+    return CORAL_OK;
+}
+
+int coral_build_begin_from_graph(coral_index_t* h) {
+    if (!h) return CORAL_ERR_ARG;
+    if (!h->d_vecs || !h->d_adj) return fail(h, CORAL_ERR_STATE, "update: vectors and graph must be set first");
+    if (int rc = ensure_device(h)) return rc;
+    if (h->building) return CORAL_OK;           // still in build mode: the edge distances are there
+    const size_t cells = (size_t)h->n * h->deg_pad;
+    if (!h->d_ndist) CK(cudaMalloc(&h->d_ndist, cells * sizeof(float)));
+    if (!h->d_deg) CK(cudaMalloc(&h->d_deg, (size_t)h->n * sizeof(int32_t)));
+    if (!h->d_claim) CK(cudaMalloc(&h->d_claim, (size_t)h->n * sizeof(uint32_t)));
+    CK(cudaMemsetAsync(h->d_claim, 0x7f, (size_t)h->n * sizeof(uint32_t), h->stream));
+    CK(coral::edge_dists(build_view(h), h->stream));
+    h->launches += 1;
+    CK(cudaStreamSynchronize(h->stream));
+    h->building = true;
+    return CORAL_OK;
+}
+
+// Lowest-numbered live node that has an out-edge and is not deleted (host scan of degrees and bits).
+static int first_usable_node(coral_index* h, int* out) {
+    std::vector<int32_t> degs((size_t)h->live_n);
+    std::vector<uint32_t> bits((size_t)((h->n + 31) / 32), 0u);
+    CK(cudaMemcpy(degs.data(), h->d_deg, degs.size() * sizeof(int32_t), cudaMemcpyDeviceToHost));
+    if (h->d_deleted) CK(cudaMemcpy(bits.data(), h->d_deleted, bits.size() * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    *out = -1;
+    for (int64_t i = 0; i < h->live_n; ++i)
+        if (degs[(size_t)i] > 0 && !((bits[(size_t)(i >> 5)] >> (i & 31)) & 1u)) {
+            *out = (int)i;
+            break;
+        }
+    return CORAL_OK;
+}
+
+int coral_delete(coral_index_t* h, const int32_t* ids, int count, int M) {
+    if (!h || (count > 0 && !ids) || count < 0) return fail(h, CORAL_ERR_ARG, "null argument");
+    if (!h->building) return fail(h, CORAL_ERR_STATE, "update: coral_build_begin_from_graph has not been called");
+    if (h->max_degree > 64) return fail(h, CORAL_ERR_LIMIT, "update: max_degree must not exceed 64");
+    if (int rc = ensure_device(h)) return rc;
+    if (count == 0) return CORAL_OK;
+    for (int i = 0; i < count; ++i)
+        if (ids[i] < 0 || (int64_t)ids[i] >= h->live_n) return fail(h, CORAL_ERR_ARG, "deleted id out of range");
+    cudaStream_t st = h->stream;
+    const size_t words = (size_t)((h->n + 31) / 32);
+    if (!h->d_deleted) {
+        CK(cudaMalloc(&h->d_deleted, words * sizeof(uint32_t)));
+        CK(cudaMemsetAsync(h->d_deleted, 0, words * sizeof(uint32_t), st));
+    }
+    int32_t *d_ids = nullptr, *d_pos = nullptr, *d_lists = nullptr, *d_piv_del = nullptr;
+    int *d_counts = nullptr, *d_offsets = nullptr;
+    cudaError_t e = cudaMalloc(&d_ids, (size_t)count * sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&d_pos, (size_t)h->n * sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&d_counts, (size_t)count * sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&d_offsets, ((size_t)count + 1) * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_ids, ids, (size_t)count * sizeof(int32_t), cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(d_pos, 0xff, (size_t)h->n * sizeof(int32_t), st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(d_counts, 0, (size_t)count * sizeof(int), st);
+    const coral::BuildGraph g = build_view(h);
+    // src/update.cu:660-672: every id of the call is marked before any repair
+    if (e == cudaSuccess) e = coral::mark_deleted(d_ids, count, h->n, h->d_deleted, d_pos, st);
+    // src/graph.cpp:155-195: the live in-neighbours of every deleted node
+    if (e == cudaSuccess) e = coral::innbr_scan(g, h->d_deleted, d_pos, d_counts, nullptr, nullptr, st);
+    std::vector<int> counts((size_t)count), offsets((size_t)count + 1, 0);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(counts.data(), d_counts, counts.size() * sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e == cudaSuccess) {
+        for (int i = 0; i < count; ++i) offsets[(size_t)i + 1] = offsets[(size_t)i] + counts[(size_t)i];
+        const int total = offsets[(size_t)count];
+        if (total > 0) {
+            e = cudaMalloc(&d_lists, (size_t)total * sizeof(int32_t));
+            if (e == cudaSuccess) e = cudaMalloc(&d_piv_del, (size_t)total * sizeof(int32_t));
+            if (e == cudaSuccess) e = cudaMemcpyAsync(d_offsets, offsets.data(), offsets.size() * sizeof(int), cudaMemcpyHostToDevice, st);
+            if (e == cudaSuccess) e = cudaMemsetAsync(d_counts, 0, (size_t)count * sizeof(int), st);
+            if (e == cudaSuccess) e = coral::innbr_scan(g, h->d_deleted, d_pos, d_counts, d_offsets, d_lists, st);
+            if (e == cudaSuccess) e = coral::sort_innbr_lists(d_lists, d_offsets, count, d_piv_del, d_ids, st);
+            h->launches += 4;
+            // src/index_gpu.cpp:170-194: deleted nodes are taken in order until their in-neighbours
+            // would exceed INNBR_BATCH = 4096 * 32 (include/uni.h:61)
+            const int kInnbrBatch = 4096 * 32;
+            int b0 = 0;
+            while (b0 < count && e == cudaSuccess) {
+                int b1 = b0, num = 0;
+                while (b1 < count && (num == 0 || num + counts[(size_t)b1] <= kInnbrBatch)) num += counts[(size_t)b1++];
+                if (num > 0)
+                    e = coral::delete_batch(g, h->d_deleted, d_piv_del + offsets[(size_t)b0], d_lists + offsets[(size_t)b0], num,
+                                            st, &h->launches);
+                b0 = b1;
+            }
+        }
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(d_ids);
+    cudaFree(d_pos);
+    cudaFree(d_counts);
+    cudaFree(d_offsets);
+    cudaFree(d_lists);
+    cudaFree(d_piv_del);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(h, CORAL_ERR_CUDA, std::string("delete: ") + cudaGetErrorString(e));
+    }
+    h->frontier_dirty = true;
+    // entry points must not be deleted nodes (Graph::update_start_ids, src/graph.cpp:229): choose them
+    // again from the lowest-numbered usable node
+    int first = -1;
+    if (int rc = first_usable_node(h, &first)) return rc;
+    if (first < 0) return fail(h, CORAL_ERR_STATE, "delete: no connected node is left");
+    return coral_index_select_start_ids(h, first, M > 0 ? M : (h->M > 0 ? h->M : 16), nullptr);
+}
+
+int coral_insert(coral_index_t* h, int64_t first_id, int count, int kb, int L, int batch, int M) {
+    if (!h || count < 0) return CORAL_ERR_ARG;
+    if (!h->building) return fail(h, CORAL_ERR_STATE, "update: coral_build_begin_from_graph has not been called");
+    if (first_id != h->live_n || first_id + count > h->n)
+        return fail(h, CORAL_ERR_ARG, "insert: the new rows must follow the live rows and fit the index");
+    if (kb < 1 || kb > 128) return fail(h, CORAL_ERR_LIMIT, "insert: need 1 <= k_b <= 128");
+    if (L <= 0) L = 512;                                              // config.json:28 test_beam_capacity
+    if (batch <= 0) batch = 2048;                                     // config.json:36 insert_batch
+    if (M <= 0) M = 16;
+    if (kb > L || M > L) return fail(h, CORAL_ERR_ARG, "insert: need k_b <= L and M <= L");
+    if (int rc = ensure_device(h)) return rc;
+    if (count == 0) return CORAL_OK;
+    batch = std::min(batch, count);
+    if (int rc = coral_search_prepare(h, batch, L, kb)) return rc;
+    int32_t *d_ins = nullptr, *d_res_ids = nullptr;
+    float* d_res_d = nullptr;
+    std::vector<int32_t> ins((size_t)count);
+    for (int i = 0; i < count; ++i) ins[(size_t)i] = (int32_t)(first_id + i);
+    cudaError_t e = cudaMalloc(&d_ins, (size_t)count * sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&d_res_ids, (size_t)batch * kb * sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&d_res_d, (size_t)batch * kb * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemcpy(d_ins, ins.data(), ins.size() * sizeof(int32_t), cudaMemcpyHostToDevice);
+    int rc = CORAL_OK;
+    const coral::BuildGraph g = build_view(h);
+    for (int s = 0; s < count && e == cudaSuccess && rc == CORAL_OK; s += batch) {        // src/index_gpu.cpp:212-216
+        const int nb = std::min(batch, count - s);
+        int first = -1;
+        rc = first_usable_node(h, &first);
+        if (rc != CORAL_OK) break;
+        if (first < 0) {
+            rc = fail(h, CORAL_ERR_STATE, "insert: no connected node to search from");
+            break;
+        }
+        rc = coral_index_select_start_ids(h, first, M, nullptr);                           // src/update.cu:777
+        if (rc != CORAL_OK) break;
+        // the new vectors are rows of the vector array: they are their own queries (src/update.cu:813)
+        rc = enqueue_search(h, h->d_vecs + (size_t)(first_id + s) * h->dim, nb, L, kb, d_res_ids, d_res_d, nullptr, h->stream);
+        if (rc != CORAL_OK) break;
+        e = cudaStreamSynchronize(h->stream);
+        if (e != cudaSuccess) break;
+        rc = coral_search_check(h);
+        if (rc != CORAL_OK) break;
+        e = coral::ce_batch(g, d_ins + s, nb, d_res_ids, d_res_d, kb, h->stream, &h->launches, 3);   // src/update.cu:904-940
+        if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
+        h->live_n = first_id + s + nb;
+        h->frontier_dirty = true;
+    }
+    cudaFree(d_ins);
+    cudaFree(d_res_ids);
+    cudaFree(d_res_d);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(h, CORAL_ERR_CUDA, std::string("insert: ") + cudaGetErrorString(e));
     }
     return rc;
 }

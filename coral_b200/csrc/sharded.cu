@@ -190,7 +190,7 @@ int coral_search_sharded(coral_index_t* h, coral_comm_t* c, const int32_t* d_id_
     if (Q == 0) return CORAL_OK;
     if (!is_device_ptr(d_queries) || (d_id_map && !is_device_ptr(d_id_map)))
         return comm_fail(c, CORAL_ERR_ARG, "queries and id map must be device pointers");
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaStream_t st = static_cast<cudaStream_t>(stream ? stream : coral_index_stream(h));
     const size_t cells = (size_t)Q * k;
     int lo = 0, hi = 0;
     coral_query_slice(Q, c->world, c->rank, &lo, &hi);

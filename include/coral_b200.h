@@ -108,6 +108,10 @@ int coral_index_set_start_ids(coral_index_t* h, const int32_t* ids, int M);
  * freed before returning. */
 int coral_index_select_start_ids(coral_index_t* h, int first_id, int M, int32_t* ids_out);
 
+/* The handle's own stream (a cudaStream_t, created non-blocking): what NULL stream arguments of
+ * this library mean.  Replaces GPUFuncs::get_stream (include/gpufuncs.cuh:607). */
+void* coral_index_stream(coral_index_t* h);
+
 /* Reads the installed graph back: adjacency [n][deg_pad] to a host or device buffer (replaces the
  * device-to-host copy of Graph::write_back_all_gpu_slots behind save_build, include/graph.cuh:481),
  * and the entry points (returns how many are installed; copies at most `capacity` to ids_out, which
@@ -262,6 +266,36 @@ int coral_build_connect_enhance(coral_index_t* h, int kb, int L, int search_batc
 int coral_build_get_graph(coral_index_t* h, int32_t* adj_out, float* dists_out, int32_t* degs_out);
 int coral_build_set_graph(coral_index_t* h, const int32_t* adj, const float* dists, const int32_t* degs);
 
+/* ---- update: delete with topology repair, insert (src/index_gpu.cpp:138-224) ----
+ * Rows [0, live) of the vector array are the index; rows [live, n) hold vectors that are not
+ * inserted yet (the reference keeps inserted vectors behind the base the same way,
+ * src/graph.cpp:264-287).  coral_index_set_live declares `live` before a build over a prefix. */
+int coral_index_set_live(coral_index_t* h, int64_t live);
+
+/* Enters update mode on a searchable index: computes the distance of every stored edge and the
+ * degrees (the reference keeps them in its Slot, include/disk_graph.h:34) unless a build is still
+ * open.  Leave with coral_build_end. */
+int coral_build_begin_from_graph(coral_index_t* h);
+
+/* Replaces IndexGPU::Delete (src/index_gpu.cpp:138-206) + GPUFuncs::vector_delete
+ * (src/update.cu:674-771): marks `count` ids (host) deleted -- the bitset of
+ * coral_index_set_deleted -- finds their live in-neighbours on the GPU (the reference keeps host
+ * hash sets, src/graph.cpp:139-195), and repairs every in-neighbour in batches of 131072: its
+ * surviving neighbours plus the deleted node's surviving out-neighbours, sorted closest-first,
+ * occlusion-pruned, kept ones first then pruned ones.  The first (deleted node, in-neighbour) pair
+ * of a batch repairs an in-neighbour (reference: thread arrival); in-neighbours are taken in
+ * ascending id order.  Then M entry points (0 = as many as installed) are chosen again
+ * (coral_index_select_start_ids) from the lowest-numbered live, undeleted, connected node. */
+int coral_delete(coral_index_t* h, const int32_t* ids, int count, int M);
+
+/* Replaces IndexGPU::Insert (src/index_gpu.cpp:207-224) + GPUFuncs::vector_insert with neighbours
+ * from the search (src/update.cu:880-959, upd_type 1): rows [first_id, first_id + count) --
+ * first_id must be the current live count -- become nodes, `batch` (0 = 2048) at a time: entry
+ * points re-chosen, each new vector searched with beam capacity L (0 = 512) for kb neighbours,
+ * reverse edges into the found nodes (src/update.cu:143-191), the new node's own row from its
+ * pruned candidates.  Calls coral_search_prepare (batch, L, kb). */
+int coral_insert(coral_index_t* h, int64_t first_id, int count, int kb, int L, int batch, int M);
+
 /* Replaces GPUFuncs::Build_Free: releases the edge distances and build scratch; the adjacency
  * (and the installed entry points) stay for searching. */
 int coral_build_end(coral_index_t* h);
@@ -313,7 +347,8 @@ void coral_query_slice(int Q, int world, int rank, int* lo, int* hi);
  * NULL = ids are global already) -> one ncclAllGather of ids and distances in a single buffer
  * -> merge by (distance, id) of THIS rank's slice of the batch (coral_query_slice): ids_out /
  * dists_out (nullable) receive (hi - lo) * k entries, host or device pointers.  Everything is
- * enqueued on `stream`; the call synchronises only when it has to copy to host buffers.
+ * enqueued on `stream` (NULL = the handle's stream); the call synchronises only when it has to
+ * copy to host buffers.
  * Communication buffers are grown on demand and kept.  world * k <= 4096. */
 int coral_search_sharded(coral_index_t* h, coral_comm_t* c, const int32_t* d_id_map, const float* d_queries,
                          int Q, int L, int k, int32_t* ids_out, float* dists_out, void* stream);

@@ -70,6 +70,14 @@ def _load():
         _lib.coral_oracle_ce_batch.restype = C.c_int
         _lib.coral_oracle_ce_batch.argtypes = [f32p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, i32p, f32p, i32p,
                                                i32p, C.c_int, i32p, f32p, C.c_int]
+        _lib.coral_oracle_delete_batch.restype = C.c_int
+        _lib.coral_oracle_delete_batch.argtypes = [f32p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, i32p, f32p, i32p,
+                                                   C.POINTER(C.c_uint32), i32p, i32p, C.c_int]
+        _lib.coral_oracle_insert_batch.restype = C.c_int
+        _lib.coral_oracle_insert_batch.argtypes = [f32p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, i32p, f32p, i32p,
+                                                   i32p, C.c_int, i32p, C.c_int]
+        _lib.coral_oracle_edge_dists.restype = C.c_int
+        _lib.coral_oracle_edge_dists.argtypes = [f32p, C.c_int64, C.c_int, C.c_int, i32p, C.c_int, f32p, i32p]
         _lib.coral_oracle_recall.restype = C.c_double
         _lib.coral_oracle_recall.argtypes = [i32p, i32p, C.c_int, C.c_int, C.c_int]
         _set_cpu_sig(_lib)
@@ -223,6 +231,99 @@ def ce_batch(base, state, iso_ids, res_ids, res_dists, metric):
                                    state.deg.ctypes.data_as(i32p), ip_, len(iso_ids), rp, dp, res_ids.shape[1])
     if rc != 0:
         raise ValueError(f"coral_oracle_ce_batch failed with {rc}")
+
+
+def state_from_adjacency(base, adj, max_degree, metric):
+    """BuildState of a finished graph: edge distances recomputed, degrees counted."""
+    lib = _load()
+    base, bp = _f32(base)
+    st = BuildState(base.shape[0], max_degree)
+    st.adj = np.ascontiguousarray(adj, np.int32).copy()
+    i32p, f32p = C.POINTER(C.c_int32), C.POINTER(C.c_float)
+    lib.coral_oracle_edge_dists(bp, base.shape[0], base.shape[1], metric_id(metric), st.adj.ctypes.data_as(i32p),
+                                st.deg_pad, st.ndist.ctypes.data_as(f32p), st.deg.ctypes.data_as(i32p))
+    return st
+
+
+def _first_usable(st, dead, live):
+    ok = (st.deg[:live] > 0) & ~dead[:live]
+    return int(np.nonzero(ok)[0][0])
+
+
+def delete_nodes(base, st, dead, del_ids, metric, n_start=16, live=None, innbr_batch=4096 * 32):
+    """IndexGPU::Delete (src/index_gpu.cpp:138-206): marks, repairs the live in-neighbours in batches,
+    re-chooses the entry points.  `dead` (bool [n]) is updated in place.  Returns the start ids."""
+    lib = _load()
+    base, bp = _f32(base)
+    n = base.shape[0]
+    live = n if live is None else live
+    del_ids = np.ascontiguousarray(del_ids, np.int32)
+    dead[del_ids] = True
+    bits = np.packbits(dead, bitorder="little")
+    bits = np.concatenate([bits, np.zeros((-len(bits)) % 4, np.uint8)]).view(np.uint32).copy()
+    # live in-neighbours of every deleted node of this call, ascending
+    rows, cols = np.nonzero((st.adj >= 0) & (np.arange(st.deg_pad)[None, :] < st.deg[:, None]) & ~dead[:, None])
+    tgt = st.adj[rows, cols]
+    pos_of = np.full(n, -1, np.int64)
+    pos_of[del_ids] = np.arange(len(del_ids))
+    sel = pos_of[tgt] >= 0
+    rows, tgt = rows[sel], tgt[sel]
+    order = np.lexsort((rows, pos_of[tgt]))
+    piv_in, piv_pos = rows[order].astype(np.int32), pos_of[tgt][order]
+    counts = np.bincount(piv_pos, minlength=len(del_ids))
+    offsets = np.concatenate([[0], np.cumsum(counts)])
+    i32p, f32p = C.POINTER(C.c_int32), C.POINTER(C.c_float)
+    b0 = 0
+    while b0 < len(del_ids):
+        b1, num = b0, 0
+        while b1 < len(del_ids) and (num == 0 or num + counts[b1] <= innbr_batch):
+            num += counts[b1]
+            b1 += 1
+        if num > 0:
+            lo, hi = offsets[b0], offsets[b1]
+            pin = np.ascontiguousarray(piv_in[lo:hi])
+            pdel = np.ascontiguousarray(del_ids[piv_pos[lo:hi]])
+            rc = lib.coral_oracle_delete_batch(bp, n, base.shape[1], metric_id(metric), st.max_degree, st.deg_pad,
+                                               st.adj.ctypes.data_as(i32p), st.ndist.ctypes.data_as(f32p),
+                                               st.deg.ctypes.data_as(i32p), bits.ctypes.data_as(C.POINTER(C.c_uint32)),
+                                               pdel.ctypes.data_as(i32p), pin.ctypes.data_as(i32p), int(hi - lo))
+            if rc != 0:
+                raise ValueError("coral_oracle_delete_batch failed")
+        b0 = b1
+    return select_start_ids(st.adj, _first_usable(st, dead, live), n_start)
+
+
+def search_hiding(base, adj, start, queries, L, k, metric, dead):
+    """The search with the deleted bitset (src/search_gpu.cu:716): the beam's ids with deleted ones dropped."""
+    ids, d, stt = search(base, adj, start, queries, L, L, metric)
+    out = np.full((len(queries), k), -1, np.int32)
+    for r in range(len(queries)):
+        keep = ids[r][(ids[r] >= 0)]
+        keep = keep[~dead[keep]][:k]
+        out[r, :len(keep)] = keep
+    return out
+
+
+def insert_nodes(base, st, dead, first_id, count, kb, metric, L=512, batch=2048, n_start=16):
+    """IndexGPU::Insert with neighbours from the search (src/index_gpu.cpp:207-224, src/update.cu:880-959)."""
+    lib = _load()
+    base, bp = _f32(base)
+    n = base.shape[0]
+    i32p, f32p = C.POINTER(C.c_int32), C.POINTER(C.c_float)
+    start, live = None, first_id
+    for s in range(0, count, batch):
+        nb = min(batch, count - s)
+        ins = np.arange(first_id + s, first_id + s + nb, dtype=np.int32)
+        start = select_start_ids(st.adj, _first_usable(st, dead, live), n_start)
+        res = search_hiding(base, st.adj, start, base[ins], L, kb, metric, dead)
+        rc = lib.coral_oracle_insert_batch(bp, n, base.shape[1], metric_id(metric), st.max_degree, st.deg_pad,
+                                           st.adj.ctypes.data_as(i32p), st.ndist.ctypes.data_as(f32p),
+                                           st.deg.ctypes.data_as(i32p), ins.ctypes.data_as(i32p), nb,
+                                           np.ascontiguousarray(res).ctypes.data_as(i32p), kb)
+        if rc != 0:
+            raise ValueError("coral_oracle_insert_batch failed")
+        live = first_id + s + nb
+    return start
 
 
 def build_graph(base, train_knn, metric, max_degree, batch=1024, ce=True, ce_L=256, ce_search_batch=524288,
