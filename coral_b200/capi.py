@@ -20,7 +20,7 @@ OK, ERR_ARG, ERR_STATE, ERR_CUDA, ERR_NOGPU, ERR_KERNEL, ERR_LIMIT, ERR_QUERY = 
 
 EXPORTS = (
     "coral_version", "coral_compiled_sm", "coral_plan", "coral_index_create", "coral_index_destroy",
-    "coral_index_set_vectors", "coral_index_attach_vectors", "coral_index_set_slots",
+    "coral_index_set_vectors", "coral_index_write_vectors", "coral_index_attach_vectors", "coral_index_set_slots",
     "coral_index_set_adjacency", "coral_index_set_start_ids", "coral_index_select_start_ids",
     "coral_index_get_adjacency", "coral_index_get_start_ids", "coral_index_stream",
     "coral_index_set_deleted",
@@ -31,7 +31,7 @@ EXPORTS = (
     "coral_build_get_graph", "coral_build_set_graph", "coral_build_end", "coral_index_set_live",
     "coral_build_begin_from_graph", "coral_delete", "coral_insert", "coral_merge_shards",
     "coral_merge_shards_strided", "coral_comm_unique_id", "coral_comm_create", "coral_comm_create_all",
-    "coral_comm_destroy", "coral_comm_world", "coral_comm_rank", "coral_comm_last_error", "coral_query_slice",
+    "coral_comm_set_id_map", "coral_comm_destroy", "coral_comm_world", "coral_comm_rank", "coral_comm_last_error", "coral_query_slice",
     "coral_search_sharded",
     "coral_map_ids", "coral_last_error", "coral_search_static", "coral_search_static_status",
 )
@@ -65,6 +65,7 @@ def load():
         "coral_index_destroy": (C.c_int, [vp]),
         "coral_index_set_vectors": (C.c_int, [vp, f32p]),
         "coral_index_attach_vectors": (C.c_int, [vp, f32p]),
+        "coral_index_write_vectors": (C.c_int, [vp, C.c_int64, C.c_int64, f32p]),
         "coral_index_set_slots": (C.c_int, [vp, i32p, C.c_size_t, i32p, C.c_size_t]),
         "coral_index_set_adjacency": (C.c_int, [vp, i32p, C.c_int]),
         "coral_index_set_start_ids": (C.c_int, [vp, i32p, C.c_int]),
@@ -104,6 +105,7 @@ def load():
         "coral_comm_unique_id": (C.c_int, [vp]),
         "coral_comm_create": (C.c_int, [C.POINTER(vp), C.c_int, C.c_int, C.c_int, vp]),
         "coral_comm_create_all": (C.c_int, [C.POINTER(vp), C.POINTER(C.c_int), C.c_int]),
+        "coral_comm_set_id_map": (C.c_int, [vp, i32p, C.c_int64]),
         "coral_comm_destroy": (C.c_int, [vp]),
         "coral_comm_world": (C.c_int, [vp]),
         "coral_comm_rank": (C.c_int, [vp]),
@@ -184,6 +186,11 @@ class Index:
         p, k = _ptr(vecs, np.float32)
         assert tuple(k.shape) == (self.n, self.dim)
         self._check(self._lib.coral_index_set_vectors(self._h, p))
+
+    def write_vectors(self, first_row: int, vecs):
+        p, k = _ptr(vecs, np.float32)
+        assert k.shape[1] == self.dim
+        self._check(self._lib.coral_index_write_vectors(self._h, int(first_row), int(k.shape[0]), p))
 
     def attach_vectors(self, dev_vecs):
         assert _is_torch(dev_vecs) and dev_vecs.is_cuda and dev_vecs.is_contiguous()

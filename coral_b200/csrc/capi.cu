@@ -443,6 +443,21 @@ int coral_index_set_vectors(coral_index_t* h, const float* vecs) {
     return CORAL_OK;
 }
 
+int coral_index_write_vectors(coral_index_t* h, int64_t first_row, int64_t count, const float* vecs) {
+    if (!h || !vecs || first_row < 0 || count < 0 || first_row + count > h->n) return fail(h, CORAL_ERR_ARG, "rows out of range");
+    if (int rc = ensure_device(h)) return rc;
+    if (!h->d_vecs) {
+        CK(cudaMalloc(&h->d_vecs, (size_t)h->n * h->dim * sizeof(float)));
+        h->own_vecs = true;
+    }
+    if (!h->own_vecs) return fail(h, CORAL_ERR_STATE, "attached vectors are written by their owner");
+    CK(cudaMemcpyAsync(h->d_vecs + (size_t)first_row * h->dim, vecs, (size_t)count * h->dim * sizeof(float), cudaMemcpyDefault,
+                       h->stream));
+    CK(cudaStreamSynchronize(h->stream));
+    h->frontier_dirty = true;
+    return CORAL_OK;
+}
+
 int coral_index_attach_vectors(coral_index_t* h, const float* dev_vecs) {
     if (!h || !dev_vecs) return fail(h, CORAL_ERR_ARG, "null argument");
     if (((uintptr_t)dev_vecs & 15) != 0) return fail(h, CORAL_ERR_ARG, "vectors must be 16-byte aligned");
@@ -604,6 +619,7 @@ int coral_get_option(coral_index_t* h, const char* name, int* value) {
     else if (s == "frontier_size") *value = h->n_front;
     else if (s == "grid_cap") *value = h->grid_cap;
     else if (s == "deg_pad") *value = h->deg_pad;
+    else if (s == "dim") *value = h->dim;
     else if (s.rfind("plan_", 0) == 0 && h->plans.count(h->last_plan_key)) {  // plan of the most recent search
         const auto& entry = h->plans[h->last_plan_key];
         const SearchPlan& p = entry.first;

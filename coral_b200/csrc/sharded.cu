@@ -29,6 +29,10 @@ struct coral_comm {
     int32_t* d_out_ids = nullptr;   // merged slice when the caller's buffers are on the host
     float* d_out_d = nullptr;
     size_t out_cap = 0;
+    float* d_q = nullptr;           // queries staged from a host pointer
+    size_t q_cap = 0;
+    int32_t* d_id_map = nullptr;    // local -> global ids installed with coral_comm_set_id_map
+    int64_t id_map_n = 0;
     std::string err;
 };
 
@@ -84,9 +88,12 @@ void free_buffers(coral_comm* c) {
     cudaFree(c->d_recv);
     cudaFree(c->d_out_ids);
     cudaFree(c->d_out_d);
-    c->d_send = c->d_recv = c->d_out_ids = nullptr;
-    c->d_out_d = nullptr;
-    c->cap = c->out_cap = 0;
+    cudaFree(c->d_q);
+    cudaFree(c->d_id_map);
+    c->d_send = c->d_recv = c->d_out_ids = c->d_id_map = nullptr;
+    c->d_out_d = c->d_q = nullptr;
+    c->cap = c->out_cap = c->q_cap = 0;
+    c->id_map_n = 0;
 }
 
 __global__ void pack_kernel(const int32_t* __restrict__ ids, const float* __restrict__ dists,
@@ -169,6 +176,24 @@ int coral_comm_destroy(coral_comm_t* c) {
     return CORAL_OK;
 }
 
+int coral_comm_set_id_map(coral_comm_t* c, const int32_t* ids, int64_t count) {
+    if (!c || !ids || count <= 0) return comm_fail(c, CORAL_ERR_ARG, "bad argument");
+    if (cudaSetDevice(c->device) != cudaSuccess) {
+        cudaGetLastError();
+        return comm_fail(c, CORAL_ERR_NOGPU, "cudaSetDevice failed");
+    }
+    cudaFree(c->d_id_map);
+    c->d_id_map = nullptr;
+    c->id_map_n = 0;
+    if (cudaMalloc(&c->d_id_map, (size_t)count * sizeof(int32_t)) != cudaSuccess ||
+        cudaMemcpy(c->d_id_map, ids, (size_t)count * sizeof(int32_t), cudaMemcpyDefault) != cudaSuccess) {
+        cudaGetLastError();
+        return comm_fail(c, CORAL_ERR_CUDA, "id map upload failed");
+    }
+    c->id_map_n = count;
+    return CORAL_OK;
+}
+
 int coral_comm_world(coral_comm_t* c) { return c ? c->world : 0; }
 int coral_comm_rank(coral_comm_t* c) { return c ? c->rank : -1; }
 
@@ -188,9 +213,29 @@ int coral_search_sharded(coral_index_t* h, coral_comm_t* c, const int32_t* d_id_
         return comm_fail(c, CORAL_ERR_NOGPU, "cudaSetDevice failed");
     }
     if (Q == 0) return CORAL_OK;
-    if (!is_device_ptr(d_queries) || (d_id_map && !is_device_ptr(d_id_map)))
-        return comm_fail(c, CORAL_ERR_ARG, "queries and id map must be device pointers");
+    if (d_id_map && !is_device_ptr(d_id_map)) return comm_fail(c, CORAL_ERR_ARG, "the id map must be a device pointer");
+    if (!d_id_map) d_id_map = c->d_id_map;      // installed with coral_comm_set_id_map (NULL: ids are global already)
     cudaStream_t st = static_cast<cudaStream_t>(stream ? stream : coral_index_stream(h));
+    if (!is_device_ptr(d_queries)) {            // host queries: staged on the stream
+        int dim = 0;
+        if (coral_get_option(h, "dim", &dim) != CORAL_OK || dim <= 0) return comm_fail(c, CORAL_ERR_STATE, "cannot read the index dimension");
+        const size_t floats = (size_t)Q * dim;
+        if (floats > c->q_cap) {
+            cudaFree(c->d_q);
+            c->d_q = nullptr;
+            c->q_cap = 0;
+            if (cudaMalloc(&c->d_q, floats * sizeof(float)) != cudaSuccess) {
+                cudaGetLastError();
+                return comm_fail(c, CORAL_ERR_CUDA, "sharded search buffers: out of memory");
+            }
+            c->q_cap = floats;
+        }
+        if (cudaMemcpyAsync(c->d_q, d_queries, floats * sizeof(float), cudaMemcpyHostToDevice, st) != cudaSuccess) {
+            cudaGetLastError();
+            return comm_fail(c, CORAL_ERR_CUDA, "sharded search: query copy failed");
+        }
+        d_queries = c->d_q;
+    }
     const size_t cells = (size_t)Q * k;
     int lo = 0, hi = 0;
     coral_query_slice(Q, c->world, c->rank, &lo, &hi);

@@ -36,6 +36,10 @@ void IndexGPU::load_config(const std::string& config_file) {
     PC.test_beam_capacity = geti("test_beam_capacity", 512);
     PC.search_start_nodes_num = geti("search_start_nodes_num", 16);
     PC.search_in_cpu = geti("search_in_cpu", 0);
+    PC.batch = geti("batch", 1024);
+    PC.enhance_nap_batch = geti("enhance_nap_batch", 4096);
+    PC.enhance_search_batch = geti("enhance_search_batch", 524288);
+    PC.insert_batch = geti("insert_batch", 2048);
 }
 
 void IndexGPU::LoadSearchNeededData(const char* base_file, const char* sampled_query_file, DIST_METRIC m) {
@@ -62,8 +66,82 @@ void IndexGPU::upload_graph(const std::vector<int32_t>& rows, int deg_pad) {
     check(coral_index_set_adjacency(handle_, rows.data(), deg_pad), "coral_index_set_adjacency");
 }
 
+void IndexGPU::BuildGPU(size_t n_sq, float* sq_data, size_t n_bp, float* bp_data, Parameters& parameters) {
+    SetParameters(parameters);
+    const std::string cfg = parameters.Get<std::string>("config_file", std::string(""));
+    if (!cfg.empty()) load_config(cfg);
+    const int CE = parameters.Get<int>("CE", 1);
+    max_degree_ = parameters.Get<int>("max_degree");
+    k_ = parameters.Get<int>("k");
+    metric_ = parameters.Get<std::string>("dist") == "l2" ? DIST_METRIC::L2_ : DIST_METRIC::IP_;
+    const std::string graph_dir = parameters.Get<std::string>("graph_file");
+    if (own_base_) std::free(h_base_);
+    h_base_ = bp_data;
+    own_base_ = false;
+    nd_ = n_bp;
+    RunFree();
+    int rc = coral_index_create(&handle_, device_, (int64_t)nd_, (int)dimension_, max_degree_,
+                                metric_ == DIST_METRIC::L2_ ? CORAL_L2 : CORAL_IP);
+    if (rc != CORAL_OK) throw std::runtime_error(std::string("coral_index_create: ") + coral_last_error(nullptr));
+    capacity_ = nd_;
+    check(coral_index_set_vectors(handle_, h_base_), "coral_index_set_vectors");
+    std::vector<int32_t> knn(n_sq * (size_t)k_);
+    check(coral_exact_knn(handle_, sq_data, (int)n_sq, k_, knn.data(), nullptr, nullptr), "coral_exact_knn");   // src/knn.cu:174-193
+    check(coral_build_begin(handle_), "coral_build_begin");
+    check(coral_build_nap(handle_, knn.data(), (int)n_sq, k_, PC.batch), "coral_build_nap");
+    int64_t n_iso = 0;
+    if (CE)
+        check(coral_build_connect_enhance(handle_, k_, 256, PC.enhance_search_batch, PC.enhance_nap_batch,
+                                          PC.search_start_nodes_num, &n_iso),
+              "coral_build_connect_enhance");
+    coral_host::Adjacency g;
+    g.n = (int64_t)nd_;
+    int deg_pad = 0;
+    check(coral_get_option(handle_, "deg_pad", &deg_pad), "coral_get_option");
+    g.deg_pad = deg_pad;
+    g.rows.resize(nd_ * (size_t)deg_pad);
+    check(coral_index_get_adjacency(handle_, g.rows.data()), "coral_index_get_adjacency");
+    if (!CE || n_iso == 0) {   // no enhancement ran: choose the entry points now
+        int first = -1;
+        for (int64_t i = 0; i < g.n && first < 0; ++i)
+            if (g.rows[(size_t)i * g.deg_pad] >= 0) first = (int)i;
+        if (first < 0) throw std::runtime_error("BuildGPU: the graph has no edges");
+        check(coral_index_select_start_ids(handle_, first, PC.search_start_nodes_num, nullptr), "coral_index_select_start_ids");
+    }
+    start_ids_.resize((size_t)coral_index_get_start_ids(handle_, nullptr, 0));
+    coral_index_get_start_ids(handle_, start_ids_.data(), (int)start_ids_.size());
+    coral_host::graph_dir_write(graph_dir, g, start_ids_);          // Graph::save_build, include/graph.cuh:481-484
+    check(coral_build_end(handle_), "coral_build_end");
+}
+
+void IndexGPU::Delete(const std::vector<int> del_ids) {
+    if (!handle_) throw std::runtime_error("Delete: call RunPrepare first");
+    if (!updating_) {
+        check(coral_build_begin_from_graph(handle_), "coral_build_begin_from_graph");
+        updating_ = true;
+    }
+    std::vector<int32_t> ids(del_ids.begin(), del_ids.end());
+    check(coral_delete(handle_, ids.data(), (int)ids.size(), PC.search_start_nodes_num), "coral_delete");
+    prepared_q_ = prepared_L_ = prepared_k_ = 0;
+}
+
+void IndexGPU::Insert(const float* ins_vectors, int ins_num) {
+    if (!handle_) throw std::runtime_error("Insert: call RunPrepare first");
+    if (nd_ + (size_t)ins_num > capacity_) throw std::runtime_error("Insert: no room left (RunPrepare with Mode::UPD reserves it)");
+    if (!updating_) {
+        check(coral_build_begin_from_graph(handle_), "coral_build_begin_from_graph");
+        updating_ = true;
+    }
+    check(coral_index_write_vectors(handle_, (int64_t)nd_, ins_num, ins_vectors), "coral_index_write_vectors");
+    check(coral_insert(handle_, (int64_t)nd_, ins_num, PC.k, PC.test_beam_capacity, PC.insert_batch,
+                       PC.search_start_nodes_num),
+          "coral_insert");
+    nd_ += (size_t)ins_num;
+    prepared_q_ = prepared_L_ = prepared_k_ = 0;     // coral_insert sized the search scratch for its own batches
+}
+
 void IndexGPU::RunPrepare(Parameters& parameters, Mode mode, size_t n_bp, float* bp_data) {
-    if (mode != Mode::SEARCH) throw std::runtime_error("only Mode::SEARCH is available in this library");
+    if (mode != Mode::SEARCH && mode != Mode::UPD) throw std::runtime_error("RunPrepare: Mode::SEARCH or Mode::UPD (BuildGPU builds)");
     SetParameters(parameters);
     const std::string cfg = parameters.Get<std::string>("config_file", std::string(""));
     if (!cfg.empty()) load_config(cfg);
@@ -80,11 +158,14 @@ void IndexGPU::RunPrepare(Parameters& parameters, Mode mode, size_t n_bp, float*
     if (!h_base_) throw std::runtime_error("RunPrepare: base vectors have not been loaded");
 
     RunFree();
-    int rc = coral_index_create(&handle_, device_, (int64_t)nd_, (int)dimension_, max_degree_,
+    capacity_ = mode == Mode::UPD ? 2 * nd_ : nd_;
+    int rc = coral_index_create(&handle_, device_, (int64_t)capacity_, (int)dimension_, max_degree_,
                                 metric_ == DIST_METRIC::L2_ ? CORAL_L2 : CORAL_IP);
     if (rc != CORAL_OK) throw std::runtime_error(std::string("coral_index_create: ") + coral_last_error(nullptr));
-    check(coral_index_set_vectors(handle_, h_base_), "coral_index_set_vectors");
-    const coral_host::Adjacency g = coral_host::graph_dir_load(graph_dir, (int64_t)nd_, max_degree_);
+    check(coral_index_write_vectors(handle_, 0, (int64_t)nd_, h_base_), "coral_index_write_vectors");
+    check(coral_index_set_live(handle_, (int64_t)nd_), "coral_index_set_live");
+    coral_host::Adjacency g = coral_host::graph_dir_load(graph_dir, (int64_t)nd_, max_degree_);
+    if (capacity_ > nd_) g.rows.resize(capacity_ * (size_t)g.deg_pad, -1);   // rows of points still to be inserted
     upload_graph(g.rows, g.deg_pad);
     start_ids_ = coral_host::start_ids_load(graph_dir + "/graph.search_start_ids");
     if (start_ids_.empty()) {
@@ -166,6 +247,7 @@ void IndexGPU::RunFree() {
     if (handle_) coral_index_destroy(handle_);
     handle_ = nullptr;
     prepared_q_ = prepared_L_ = prepared_k_ = 0;
+    updating_ = false;
 }
 
 }  // namespace efanna2e

@@ -4,7 +4,8 @@
 // and units, so a caller of efanna2e::IndexGPU's search side compiles against
 // this header unchanged.  Differences, all on purpose: errors are thrown as
 // std::runtime_error instead of exiting the process; scratch is sized once and
-// kept between searches; build/insert/delete are not part of this library.
+// kept between searches; the build keeps no k-NN cache and runs NAP and CE in one
+// pass on one GPU (no out-of-core tiers).
 #pragma once
 #include <cstddef>
 #include <cstdint>
@@ -80,6 +81,8 @@ class Test_Result {
 struct ProConfig {
     int dim = 200, k = 100, max_degree = 32;
     int search_start_nodes_num = 16, test_beam_capacity = 512, search_in_cpu = 0;
+    // build and update keys (config.json:5-8,36)
+    int batch = 1024, enhance_nap_batch = 4096, enhance_search_batch = 524288, insert_batch = 2048;
 };
 
 class Index;  // the reference's base class is not needed by the search side
@@ -109,6 +112,17 @@ class IndexGPU {
     // Flat graph import; the file's entry point becomes the only start id
     // (src/graph.cu:709-743).
     void LoadRoarGraph(std::string filename);
+    // Builds the graph over bp_data (n_bp x dim, already normalised for inner product) from the
+    // n_sq training queries sq_data: exact k nearest base points per query, NAP, and -- CE = 1 -- the
+    // connectivity enhancement; writes the graph directory `graph_file` and its entry points
+    // (src/index_gpu.cpp:308-383).  Keys: dist, k, max_degree, CE, graph_file (optional config_file).
+    // The handle stays searchable afterwards.
+    void BuildGPU(size_t n_sq, float* sq_data, size_t n_bp, float* bp_data, Parameters& parameters);
+    // Delete with topology repair / insert with neighbours from the search (src/index_gpu.cpp:138-224).
+    // Mode::UPD in RunPrepare reserves room for as many inserted points as there are base points,
+    // as the reference does (src/graph.cpp:141-142).
+    void Delete(const std::vector<int> del_ids);
+    void Insert(const float* ins_vectors, int ins_num);
     void RunFree();
     void load_config(const std::string& config_file);
     void SetParameters(Parameters& parameters) { parameters_ = parameters; }
@@ -138,6 +152,8 @@ class IndexGPU {
     coral_index_t* handle_ = nullptr;
     std::vector<int32_t> start_ids_;
     int prepared_q_ = 0, prepared_L_ = 0, prepared_k_ = 0;
+    size_t capacity_ = 0;      // rows the handle was created for (>= nd_ in Mode::UPD)
+    bool updating_ = false;
 };
 
 }  // namespace efanna2e

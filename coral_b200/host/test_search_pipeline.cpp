@@ -12,14 +12,26 @@
 // --deleted_ids FILE (text list of ids hidden from the results, IndexGPU::SetDeleted),
 // --verify (count hits on the device with IndexGPU::Search_and_Verify, needs a
 // ground truth exactly k wide; prints "hits <n>" per sweep point).
+// Multi-GPU (one host thread and one handle per GPU, devices 0..N-1):
+//   --gpus N              the index is replicated and the batch split into N contiguous parts;
+//   --shards G --seed S   the base is split into G shards by a seeded balanced random partition,
+//                         one graph per shard under <graph_path>/shard<g> (built from
+//                         --train_path FILE with IndexGPU::BuildGPU when the directory is missing),
+//                         every shard searches every query and the per-shard top-k are merged
+//                         through one NCCL all-gather (coral_search_sharded).
 #include <algorithm>
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <fstream>
 #include <iostream>
 #include <map>
+#include <numeric>
+#include <random>
 #include <string>
+#include <sys/stat.h>
+#include <thread>
 #include <vector>
 
 #include "formats.h"
@@ -36,6 +48,158 @@ static float ComputeRecall(int q_num, int k, int gt_dim, const int* res, const i
             if (std::find(res + (size_t)i * k, res + (size_t)i * k + k, p) != res + (size_t)i * k + k) ++total;
         }
     return (float)total / (float)((long)k * q_num);
+}
+
+// Balanced random partition of n ids into G shards: shard_of[id], seeded.
+static std::vector<int> random_partition(size_t n, int G, unsigned seed) {
+    std::vector<size_t> perm(n);
+    std::iota(perm.begin(), perm.end(), (size_t)0);
+    std::mt19937_64 gen(seed);
+    std::shuffle(perm.begin(), perm.end(), gen);
+    std::vector<int> shard_of(n);
+    for (size_t i = 0; i < n; ++i) shard_of[perm[i]] = (int)(i * (size_t)G / n);
+    return shard_of;
+}
+
+static bool dir_exists(const std::string& p) {
+    struct stat st;
+    return stat(p.c_str(), &st) == 0 && S_ISDIR(st.st_mode);
+}
+
+// --shards: returns 0 on success.  Prints the same table as the single-GPU sweep.
+static int run_sharded(int G, unsigned seed, const std::string& dist, int k, int max_degree, const std::string& graph_dir,
+                       const std::string& base_path, const std::string& train_path, const std::string& config_file,
+                       const float* query_data, const coral_host::FbinMeta& qm, const coral_host::GroundTruth& gt,
+                       const std::vector<int>& L_vec) {
+    coral_host::FbinMeta bm;
+    float* base = coral_host::fbin_load(base_path, bm);
+    if (dist == "ip") coral_host::normalize_rows(base, bm.n, (size_t)bm.dim);
+    const std::vector<int> shard_of = random_partition(bm.n, G, seed);
+    std::vector<std::vector<int32_t>> ids_of((size_t)G);
+    for (size_t i = 0; i < bm.n; ++i) ids_of[(size_t)shard_of[i]].push_back((int32_t)i);
+    std::vector<std::vector<float>> vecs((size_t)G);
+    for (int g = 0; g < G; ++g) {
+        vecs[(size_t)g].resize(ids_of[(size_t)g].size() * (size_t)bm.dim);
+        for (size_t r = 0; r < ids_of[(size_t)g].size(); ++r)
+            std::memcpy(&vecs[(size_t)g][r * (size_t)bm.dim], base + (size_t)ids_of[(size_t)g][r] * bm.dim, (size_t)bm.dim * 4);
+    }
+    std::free(base);
+    coral_host::FbinMeta tm;
+    float* train = nullptr;
+    std::vector<IndexGPU*> shards((size_t)G, nullptr);
+    for (int g = 0; g < G; ++g) {
+        Parameters p;
+        p.Set<std::string>("dist", dist);
+        p.Set<int>("k", 100);
+        p.Set<int>("max_degree", max_degree);
+        p.Set<int>("CE", 1);
+        const std::string dir = graph_dir + "/shard" + std::to_string(g);
+        p.Set<std::string>("graph_file", dir);
+        p.Set<std::string>("config_file", config_file);
+        IndexGPU* ix = new IndexGPU((size_t)bm.dim, ids_of[(size_t)g].size(), dist == "l2" ? efanna2e::L2 : efanna2e::INNER_PRODUCT, nullptr);
+        ix->SetDevice(g);
+        if (dir_exists(dir)) {
+            p.Set<int>("k", k);
+            ix->RunPrepare(p, Mode::SEARCH, ids_of[(size_t)g].size(), vecs[(size_t)g].data());
+        } else {
+            if (train_path.empty()) throw std::runtime_error("no graph under " + dir + " and no --train_path to build it from");
+            if (!train) {
+                train = coral_host::fbin_load(train_path, tm);
+                if (dist == "ip") coral_host::normalize_rows(train, tm.n, (size_t)tm.dim);
+            }
+            std::cout << "Build shard " << g << ": " << ids_of[(size_t)g].size() << " points" << std::endl;
+            ix->BuildGPU(tm.n, train, ids_of[(size_t)g].size(), vecs[(size_t)g].data(), p);
+        }
+        shards[(size_t)g] = ix;
+    }
+    std::free(train);
+    std::vector<int> devices((size_t)G);
+    std::iota(devices.begin(), devices.end(), 0);
+    std::vector<coral_comm_t*> comms((size_t)G, nullptr);
+    if (coral_comm_create_all(comms.data(), devices.data(), G) != CORAL_OK)
+        throw std::runtime_error(std::string("coral_comm_create_all: ") + coral_comm_last_error(nullptr));
+    for (int g = 0; g < G; ++g)
+        if (coral_comm_set_id_map(comms[(size_t)g], ids_of[(size_t)g].data(), (int64_t)ids_of[(size_t)g].size()) != CORAL_OK)
+            throw std::runtime_error(std::string("coral_comm_set_id_map: ") + coral_comm_last_error(comms[(size_t)g]));
+    std::vector<int> res(qm.n * (size_t)k, -1);
+    const int Q = (int)qm.n;
+    std::cout << "L\t\tQPS\t\tavg_time\t\trecall@" << k << std::endl;
+    for (int L : L_vec) {
+        for (int g = 0; g < G; ++g)
+            if (coral_search_prepare(shards[(size_t)g]->handle(), Q, L, k) != CORAL_OK)
+                throw std::runtime_error(std::string("coral_search_prepare: ") + coral_last_error(shards[(size_t)g]->handle()));
+        double best = 0.0;
+        for (int rep = 0; rep < 2; ++rep) {                  // the first pass also sizes the exchange buffers
+            std::vector<std::string> errors((size_t)G);
+            std::vector<std::thread> th;
+            const auto t0 = std::chrono::steady_clock::now();
+            for (int g = 0; g < G; ++g)
+                th.emplace_back([&, g]() {
+                    int lo = 0, hi = 0;
+                    coral_query_slice(Q, G, g, &lo, &hi);
+                    const int rc = coral_search_sharded(shards[(size_t)g]->handle(), comms[(size_t)g], nullptr, query_data, Q, L, k,
+                                                        res.data() + (size_t)lo * k, nullptr, nullptr);
+                    if (rc != CORAL_OK) errors[(size_t)g] = coral_comm_last_error(comms[(size_t)g]);
+                });
+            for (auto& t : th) t.join();
+            best = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+            for (const auto& e : errors)
+                if (!e.empty()) throw std::runtime_error("coral_search_sharded: " + e);
+        }
+        const int nq = std::min<int>(Q, gt.nq);
+        const float recall = ComputeRecall(nq, k, gt.k, res.data(), gt.ids.data());
+        std::cout << L << "\t\t" << Q / best << "\t\t" << best << "\t\t" << recall << std::endl;
+    }
+    for (auto* c : comms) coral_comm_destroy(c);
+    for (auto* ix : shards) delete ix;
+    return 0;
+}
+
+// --gpus N: N replicas, the batch split into contiguous parts, one host thread per GPU.
+static int run_replicated(int N, Parameters& parameters, const std::string& dist, int k, const std::string& base_path,
+                          const float* query_data, const coral_host::FbinMeta& qm, const coral_host::GroundTruth& gt,
+                          const std::vector<int>& L_vec) {
+    std::vector<IndexGPU*> reps((size_t)N, nullptr);
+    for (int g = 0; g < N; ++g) {
+        reps[(size_t)g] = new IndexGPU((size_t)qm.dim, 0, dist == "l2" ? efanna2e::L2 : efanna2e::INNER_PRODUCT, nullptr);
+        reps[(size_t)g]->SetDevice(g);
+        reps[(size_t)g]->LoadSearchNeededData(base_path.c_str(), "", dist == "l2" ? DIST_METRIC::L2_ : DIST_METRIC::IP_);
+        reps[(size_t)g]->RunPrepare(parameters, Mode::SEARCH);
+    }
+    const int Q = (int)qm.n;
+    std::vector<int> res((size_t)Q * k, -1);
+    std::cout << "L\t\tQPS\t\tavg_time\t\trecall@" << k << "\t\tavg_hops" << std::endl;
+    for (int L : L_vec) {
+        std::vector<float> secs((size_t)N, 0.f);
+        std::vector<size_t> hops((size_t)N, 0);
+        std::vector<std::string> errors((size_t)N);
+        for (int rep = 0; rep < 2; ++rep) {                  // the first pass sizes the scratch
+            std::vector<std::thread> th;
+            for (int g = 0; g < N; ++g)
+                th.emplace_back([&, g]() {
+                    try {
+                        int lo = 0, hi = 0;
+                        coral_query_slice(Q, N, g, &lo, &hi);
+                        const Test_Result tr = reps[(size_t)g]->Search(query_data + (size_t)lo * qm.dim, hi - lo, L,
+                                                                       res.data() + (size_t)lo * k);
+                        secs[(size_t)g] = tr.get_time();
+                        hops[(size_t)g] = tr.get_hops();
+                    } catch (const std::exception& ex) {
+                        errors[(size_t)g] = ex.what();
+                    }
+                });
+            for (auto& t : th) t.join();
+            for (const auto& e : errors)
+                if (!e.empty()) throw std::runtime_error(e);
+        }
+        const float time = *std::max_element(secs.begin(), secs.end());      // the slowest GPU's kernel window
+        const size_t total_hops = std::accumulate(hops.begin(), hops.end(), (size_t)0);
+        const int nq = std::min<int>(Q, gt.nq);
+        const float recall = ComputeRecall(nq, k, gt.k, res.data(), gt.ids.data());
+        std::cout << L << "\t\t" << Q / time << "\t\t" << time << "\t\t" << recall << "\t\t" << (float)total_hops / Q << std::endl;
+    }
+    for (auto* ix : reps) delete ix;
+    return 0;
 }
 
 int main(int argc, char** argv) {
@@ -98,6 +262,26 @@ int main(int argc, char** argv) {
         parameters.Set<std::string>("log_file", str("log_file", ""));
         parameters.Set<std::string>("config_file", str("config_file", ""));
 
+        if (L_vec.empty() && max_recall > 0.5) L_vec.push_back(128);   // :279-281
+        const int n_shards = std::atoi(str("shards", "0").c_str()), n_gpus = std::atoi(str("gpus", "1").c_str());
+        if (n_shards > 0) {
+            for (int L : L_vec)
+                if (k > L) {
+                    std::cout << "L must greater or equal than k" << std::endl;
+                    return 1;
+                }
+            const int rc = run_sharded(n_shards, (unsigned)std::atol(str("seed", "20260004").c_str()), dist, k, max_degree, graph_dir,
+                                       str("base_data_path", ""), str("train_path", ""), str("config_file", ""), query_data, qm,
+                                       gt, L_vec);
+            std::free(query_data);
+            return rc;
+        }
+        if (n_gpus > 1) {
+            const int rc = run_replicated(n_gpus, parameters, dist, k, str("base_data_path", ""), query_data, qm, gt, L_vec);
+            std::free(query_data);
+            return rc;
+        }
+
         IndexGPU index((size_t)qm.dim, 0, dist == "l2" ? efanna2e::L2 : efanna2e::INNER_PRODUCT, nullptr);
         index.SetDevice(std::atoi(str("device", "0").c_str()));
         index.LoadSearchNeededData(str("base_data_path", "").c_str(), "",
@@ -121,7 +305,6 @@ int main(int argc, char** argv) {
             csv << "L, QPS, time, recall@" << k << ", avg_hops" << std::endl;
         }
         std::cout << "L\t\tQPS\t\tavg_time\t\trecall@" << k << "\t\tavg_hops" << std::endl;
-        if (L_vec.empty() && max_recall > 0.5) L_vec.push_back(128);
         for (size_t i = 0; i < L_vec.size(); ++i) {
             const int L = L_vec[i];
             if (k > L) {

@@ -75,6 +75,11 @@ int coral_index_destroy(coral_index_t* h);
  * may be a host or a device pointer to n*dim floats; the data is copied. */
 int coral_index_set_vectors(coral_index_t* h, const float* vecs);
 
+/* Writes rows [first_row, first_row + count) of the handle's own vector array (allocating it for n
+ * rows on first use): how vectors to be inserted later reach the device.  Replaces the copy in
+ * Graph::insert_nodes (src/graph.cpp:277-279).  Host or device pointer. */
+int coral_index_write_vectors(coral_index_t* h, int64_t first_row, int64_t count, const float* vecs);
+
 /* Same, without the copy: `dev_vecs` must stay valid (and 16-byte aligned)
  * for the life of the handle.  No counterpart in the reference. */
 int coral_index_attach_vectors(coral_index_t* h, const float* dev_vecs);
@@ -195,7 +200,7 @@ int64_t coral_launch_count(coral_index_t* h);
  *                            1 = always, -1 = never
  * coral_get_option also answers "plan_stages", "plan_warps", "plan_chunk_bytes",
  * "plan_smem_bytes", "plan_hash_bits", "plan_ctas_per_sm" (the plan of the most recent search or
- * prepare), "last_cluster_size", "last_scheduled", "frontier_size", "grid_cap", "deg_pad".
+ * prepare), "last_cluster_size", "last_scheduled", "frontier_size", "grid_cap", "deg_pad", "dim".
  * Returns CORAL_ERR_ARG for unknown names. */
 int coral_set_option(coral_index_t* h, const char* name, int value);
 int coral_get_option(coral_index_t* h, const char* name, int* value);
@@ -334,6 +339,9 @@ int coral_comm_unique_id(void* id128);
 int coral_comm_create(coral_comm_t** out, int device, int world, int rank, const void* id128);
 /* n communicators for n GPUs driven by ONE process (out: n pointers); ranks = positions. */
 int coral_comm_create_all(coral_comm_t** out, const int* devices, int n);
+/* Installs this rank's local -> global id map (count ints, host or device; copied): used by
+ * coral_search_sharded when its d_id_map argument is NULL. */
+int coral_comm_set_id_map(coral_comm_t* c, const int32_t* ids, int64_t count);
 int coral_comm_destroy(coral_comm_t* c);
 int coral_comm_world(coral_comm_t* c);
 int coral_comm_rank(coral_comm_t* c);
@@ -342,9 +350,9 @@ const char* coral_comm_last_error(coral_comm_t* c);
 /* Rows [*lo, *hi) of a Q-query batch that `rank` of `world` owns (contiguous, balanced). */
 void coral_query_slice(int Q, int world, int rank, int* lo, int* hi);
 
-/* Sharded search, collective over the communicator: the same Q queries (device pointer) on
- * every rank.  Local search (as coral_search_async) -> global ids through d_id_map (device,
- * NULL = ids are global already) -> one ncclAllGather of ids and distances in a single buffer
+/* Sharded search, collective over the communicator: the same Q queries (host or device pointer) on
+ * every rank.  Local search (as coral_search_async) -> global ids through d_id_map (device; NULL =
+ * the map installed with coral_comm_set_id_map, or global ids already) -> one ncclAllGather of ids and distances in a single buffer
  * -> merge by (distance, id) of THIS rank's slice of the batch (coral_query_slice): ids_out /
  * dists_out (nullable) receive (hi - lo) * k entries, host or device pointers.  Everything is
  * enqueued on `stream` (NULL = the handle's stream); the call synchronises only when it has to

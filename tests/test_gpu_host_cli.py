@@ -154,3 +154,38 @@ def test_driver_flat_graph_import_deleted_ids_and_device_hit_count(tmp_path):
     hits = [int(ln.split()[1]) for ln in r.stdout.splitlines() if ln.startswith("hits ")]
     expect = sum(sum(1 for p in gt[qi] if p in ids[qi]) for qi in range(len(c.queries)))
     assert hits == [expect]
+
+
+def test_driver_shards_builds_per_shard_graphs_and_merges_through_nccl(tmp_path):
+    """--shards 1 --seed S --train_path F: the driver partitions the base, builds the shard's graph
+    with IndexGPU::BuildGPU (exact lists -> NAP -> CE), writes it in the reference's directory
+    layout, searches through coral_search_sharded (a one-rank NCCL communicator), and a second run
+    loads the saved graph instead of building -- same ids both times, good recall."""
+    import torch
+    from coral_b200 import synth
+    build_host.build()
+    n, dim, k = 8000, 64, 10
+    ds = synth.make_l2_mixture(n, 2000, 64, dim=dim, centers=8, seed=21, rot_dims=60, latent_dim=8, latent_jitter=0.5)
+    base, train, q = ds.base.numpy(), ds.train.numpy(), ds.test.numpy()
+    for name, arr in (("base", base), ("train", train), ("query", q)):
+        (tmp_path / f"{name}.fbin").write_bytes(struct.pack("<ii", *arr.shape) + arr.tobytes())
+    gt, _ = oracle.exact_knn(base, q, 100, "l2")
+    (tmp_path / "gt.bin").write_bytes(struct.pack("<ii", gt.shape[0], gt.shape[1]) + gt.astype(np.int32).tobytes())
+    (tmp_path / "config.json").write_text('{"dim": %d, "k": 100, "batch": 256, "enhance_search_batch": 2048, '
+                                          '"enhance_nap_batch": 512}' % dim)
+    os.makedirs(tmp_path / "graph")
+    exe = os.path.join(os.path.dirname(build_host.HOST_LIB), "test_search_pipeline")
+    cmd = [exe, "--dataset", "synthetic", "--data_type", "float", "--dist", "l2",
+           "--base_data_path", str(tmp_path / "base.fbin"), "--query_path", str(tmp_path / "query.fbin"),
+           "--gt_path", str(tmp_path / "gt.bin"), "--graph_path", str(tmp_path / "graph"),
+           "--train_path", str(tmp_path / "train.fbin"), "--config_file", str(tmp_path / "config.json"),
+           "--max_degree", "32", "--k", str(k), "--L", "64", "--shards", "1", "--seed", "7"]
+    outs = []
+    for run in range(2):
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout + r.stderr
+        assert ("Build shard 0" in r.stdout) == (run == 0)
+        row = [ln.split() for ln in r.stdout.splitlines() if ln.startswith("64")][-1]
+        outs.append(float(row[3]))
+    assert os.path.exists(tmp_path / "graph" / "shard0" / "graph.search_start_ids")
+    assert outs[0] == outs[1] and outs[0] >= 0.9
