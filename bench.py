@@ -110,18 +110,21 @@ class ClockSampler:
                 "samples": len(clocks)}
 
 
-def build_index(w, local, rank=0, seed=20260001, n_test=None):
+def build_index(w, local, rank=0, seed=20260001, n_test=None, extra=0):
     """Seeded synthetic data of the workload and the index over it, built by the library on this GPU
-    (of this rank's shard when sharded).  Returns (dataset, index handle, build info)."""
+    (of this rank's shard when sharded).  `extra` more points of the same distribution are kept behind
+    the indexed rows, to be inserted later.  Returns (dataset, index handle, build info)."""
     import torch
     from coral_b200 import capi, synth
     t0 = time.time()
     draw = seed + 1000 + rank if w.get("sharded") else None
     cfg = synth.CONFIGS[w["data"]]
-    ds = synth.make_config(w["data"], w["train"], n_test or w["q"], n=w["n"], seed=seed, device=f"cuda:{local}",
+    ds = synth.make_config(w["data"], w["train"], n_test or w["q"], n=w["n"] + extra, seed=seed, device=f"cuda:{local}",
                            draw_seed=draw)
-    ix = capi.Index(w["n"], cfg["dim"], cfg["deg"], cfg["kind"], device=local)
+    ix = capi.Index(w["n"] + extra, cfg["dim"], cfg["deg"], cfg["kind"], device=local)
     ix.attach_vectors(ds.base)
+    if extra:
+        ix.set_live(w["n"])
     t1 = time.time()
     info = ix.build(ds.train, kb=100)
     torch.cuda.synchronize()
@@ -254,21 +257,32 @@ def run_latency(args, w, ix, ds, device, rank):
         return table
 
     table = measure()
-    # The same batches with 10 % of the points deleted (tombstones: the reference's deleted-bitset
-    # overload hides them from the results, src/search_gpu.cu:716).
+    # Second leg: 10 % of the points deleted with topology repair, then 5 % new points inserted with
+    # neighbours from the same search kernel at L = 128 (src/index_gpu.cpp:138-224), then the same batches.
+    n, extra = w["n"], w["n"] // 20
     rng = np.random.default_rng(77)
-    dead = rng.random(w["n"]) < 0.10
-    bits = np.packbits(dead, bitorder="little")
-    bits = np.concatenate([bits, np.zeros((-len(bits)) % 4, np.uint8)]).view(np.uint32)
-    gt_wide = ix.exact_knn(ds.test[:n_gt], 4 * k, dists=False)[0].cpu().numpy()
+    del_ids = rng.choice(n, n // 10, replace=False).astype(np.int32)
+    dead = np.zeros(n + extra, bool)
+    dead[del_ids] = True
+    t0 = time.time()
+    ix.update_begin()
+    ix.delete(del_ids)
+    torch.cuda.synchronize()
+    t_del = time.time() - t0
+    t0 = time.time()
+    ix.insert(n, extra, kb=100, L=128, batch=32768)
+    torch.cuda.synchronize()
+    t_ins = time.time() - t0
+    ix.build_end()
+    ix.prepare(max(w["q"], n_gt), L, 4 * k)
+    gt_wide = ix.exact_knn(ds.test[:n_gt], 4 * k, dists=False)[0].cpu().numpy()      # over all live rows
     gt_alive = np.stack([row[~dead[row]][:k] for row in gt_wide])
-    ix.set_deleted(bits)
     ids_d, _, _, _ = ix.search(ds.test[:n_gt], L, k, dists=False)
     ids_d = ids_d.cpu().numpy() if hasattr(ids_d, "cpu") else np.asarray(ids_d)
     assert not dead[ids_d[ids_d >= 0]].any(), "a deleted id was returned"
     recall_deleted = float(np.mean([len(set(a) & set(b)) / k for a, b in zip(ids_d, gt_alive)]))
+    inserted_found = float(np.mean((ids_d >= n).any(1)))
     table_deleted = measure()
-    ix.set_deleted(None)
     if rank == 0:
         b1 = table[w["latency"][0]]
         out = {"metric": "p50 latency of one query batch, 10Mx512 IP, L=%d" % L, "value": b1["p50_us"], "unit": "us",
@@ -276,7 +290,10 @@ def run_latency(args, w, ix, ds, device, rank):
                "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                "config": {"workload": args.workload, "n": w["n"], "dim": dim, "metric": cfg["kind"], "max_degree": cfg["deg"],
                           "k": k, "L": L, "recall": recall, "batch_sizes": w["latency"], "latency": table,
-                          "latency_with_10pct_tombstones": table_deleted, "recall_with_10pct_tombstones": recall_deleted,
+                          "after_10pct_delete_with_repair_and_5pct_insert": {
+                              "latency": table_deleted, "recall": recall_deleted, "delete_s": round(t_del, 1),
+                              "insert_s": round(t_ins, 1), "insert_batch": 32768,
+                              "queries_with_an_inserted_point_in_their_top_k": inserted_found},
                           "l2_policy": "inputs larger than L2; every batch uses different queries"},
                "e2e": {"value": b1["e2e_p50_us"], "unit": "us", "h2d_bytes_per_step": dim * 4 * w["latency"][0],
                        "d2h_bytes_per_step": k * 4 * w["latency"][0] + 32},
@@ -450,7 +467,8 @@ def main():
         return float(t.item())
 
     cfg = synth.CONFIGS[w["data"]]
-    ds, ix, build_info = build_index(w, local, rank)     # replicated: same seed on every rank; sharded: own shard
+    extra_rows = w["n"] // 20 if w.get("latency") else 0
+    ds, ix, build_info = build_index(w, local, rank, extra=extra_rows)   # replicated: same seed on every rank; sharded: own shard
     Q, k, dim = w["q"], w["k"], cfg["dim"]
     for kv in args.option:
         name, val = kv.split("=")
