@@ -53,7 +53,7 @@ METRIC = "QPS @ recall@10>=0.95, 10Mx512 IP"
 PEAK_FALLBACK_GBS = 6650.0
 # DRAM bytes per algorithmic byte of the search kernel, from the ncu captures summarised under
 # profiles/ (a profile constant, not a measurement of this run): workload -> ratio.
-DRAM_PER_ALGORITHMIC_BYTE = {}
+DRAM_PER_ALGORITHMIC_BYTE = {"small": 0.73}
 
 
 def log(*a):

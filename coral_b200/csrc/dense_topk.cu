@@ -27,8 +27,8 @@
 // and tightens the threshold.  After the first few tiles almost nothing passes (about k' ln(N/k')
 // appends per row in total).
 //
-// Every wait is bounded (clock limit -> error flag, the CTA drains and frees its TMEM).  No TMA
-// multicast, no clusters.
+// Every wait is bounded (clock limit -> error flag, the CTA drains and frees its TMEM).  Every CTA
+// loads its own tiles; no clusters.
 #include "dense_topk.cuh"
 
 #include <cuda.h>
