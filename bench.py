@@ -50,6 +50,19 @@ WORKLOADS = {
     "c5": dict(data="c3", n=10_000_000, q=8_192, k=10, Ls=[128], train=100_000, latency=[1, 8, 64, 512]),
 }
 METRIC = "QPS @ recall@10>=0.95, 10Mx512 IP"
+
+
+def metric_name(workload, w):
+    """The headline metric's name for the workload it is quoted on (c3 and its small-batch leg);
+    the other workloads are named after their own shape so that a line cannot be mistaken for it."""
+    if workload in ("c3", "c5"):
+        return METRIC
+    from coral_b200 import synth
+    cfg = synth.CONFIGS[w["data"]]
+    n = w["n"]
+    size = f"{n // 1_000_000}M" if n % 1_000_000 == 0 else (f"{n / 1e6:g}M" if n >= 1_000_000 else str(n))
+    return (f"QPS @ recall@{w['k']}>=0.95, {size}x{cfg['dim']} {cfg['kind'].upper()}"
+            + (" per shard, sharded" if w.get("sharded") else ""))
 PEAK_FALLBACK_GBS = 6650.0
 # DRAM bytes per algorithmic byte of the search kernel, from the ncu captures summarised under
 # profiles/ (a profile constant, not a measurement of this run): workload -> ratio.
@@ -166,6 +179,32 @@ def cpu_reference(base_h, adj_h, start_h, queries_h, gt_h, L0, k, max_L=1024, th
                           if kind == "reference" else "self-contained port of search_in_cpu"))}
 
 
+def reference_gpu_kernel(ix, base_h, adj_h, start_h, queries_h, gt_h, L, k, metric, max_degree):
+    """The reference's own search kernel (its sources compiled unmodified for sm_100a under
+    oracle/_ref) on the same graph, entry points, queries and L, timed over the reference's own window
+    (src/search_gpu.cu:861-877).  Reported beside the CPU baseline; None when that build is absent.
+    The reference kernel reads out of range for a query whose beam never fills, so it only runs after
+    this library's search reported status 0 for every query of the sample."""
+    from oracle import oracle
+    if not oracle.have_ref_gpu():
+        return None
+    try:
+        _, _, st, _ = ix.search(queries_h, L, k, dists=False, stats=True)
+        if int(np.abs(st[:, 0]).max()) != 0:
+            return {"value": None, "unit": "queries/s", "sample": "skipped: a query of the sample did not fill its beam"}
+        best, ids = None, None
+        for _ in range(2):
+            ids, _, hops, secs = oracle.ref_gpu_search(base_h, adj_h, start_h, queries_h, L, k, metric, max_degree=max_degree)
+            best = secs if best is None else min(best, secs)
+        m = min(len(queries_h), len(gt_h))
+        return {"value": len(queries_h) / best, "unit": "queries/s", "L": L, "recall": oracle.recall(ids[:m], gt_h[:m], k),
+                "seconds": best, "hops": hops,
+                "sample": f"first {len(queries_h)} queries, best of 2 calls of GPUFuncs::search_gpu (4096 persistent CTAs x 512 threads), "
+                          "kernel + hop-count copy as the reference times it, queries and results resident on the device"}
+    except Exception as e:
+        return {"value": None, "unit": "queries/s", "sample": f"failed: {e}"}
+
+
 def run_reference(args, w, rank, world):
     """bench.py --impl reference: the reference's CPU search on this box's host cores, rank 0 only."""
     if rank != 0:
@@ -194,7 +233,7 @@ def run_reference(args, w, rank, world):
     r = reps[-1]
     cfg = synth.CONFIGS[w["data"]]
     out = {
-        "impl": "reference", "metric": METRIC, "value": qps, "unit": "queries/s", "n_gpus": args.gpus,
+        "impl": "reference", "metric": metric_name(args.workload, w), "value": qps, "unit": "queries/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sample / qps * 1e3, "higher_is_better": True,
         "scaling": "weak" if w.get("sharded") else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "n": w["n"], "dim": cfg["dim"], "metric": cfg["kind"], "max_degree": cfg["deg"],
@@ -614,8 +653,11 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
             sample = min(args.cpu_queries, Q)
-            cpu = cpu_reference(ds.base.cpu().numpy(), ix.get_adjacency(), ix.get_start_ids(), ds.test[:sample].cpu().numpy(),
-                                gt_ids[:min(sample, n_gt)].cpu().numpy(), L, k)
+            base_h, adj_h, start_h = ds.base.cpu().numpy(), ix.get_adjacency(), ix.get_start_ids()
+            q_h, g_h = ds.test[:sample].cpu().numpy(), gt_ids[:min(sample, n_gt)].cpu().numpy()
+            cpu = cpu_reference(base_h, adj_h, start_h, q_h, g_h, L, k)
+            cpu["reference_gpu_kernel"] = reference_gpu_kernel(ix, base_h, adj_h, start_h, q_h, g_h, L, k, cfg["kind"], cfg["deg"])
+            del base_h, adj_h
         except Exception as e:  # the baseline is a report, never a reason to lose the measurement
             cpu = {"value": None, "unit": "queries/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
 
@@ -644,7 +686,7 @@ def main():
     if rank == 0:
         ratio = DRAM_PER_ALGORITHMIC_BYTE.get(args.workload)
         out = {
-            "metric": METRIC, "value": Q / (dev_ms * 1e-3), "unit": "queries/s", "n_gpus": world, "steps": args.steps,
+            "metric": metric_name(args.workload, w), "value": Q / (dev_ms * 1e-3), "unit": "queries/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True,
             "scaling": "weak" if sharded_mode else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": args.workload, "n": w["n"] * (world if sharded_mode else 1), "dim": dim,

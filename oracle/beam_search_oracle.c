@@ -10,10 +10,17 @@
  *   closer-than predicate     include/utils.cuh:380-382
  *   sentinels                 include/uni.h:65-68
  *
- * Parity status: UNPINNED.  The reference ships no golden vector, known-answer
- * test or fixture for this path and its GPU sources do not build, so this file
- * is the definition the CUDA kernels are held to.  Only tests, the smoke check
- * and the benchmark's checker may load it.
+ * Parity status: PINNED to the reference's own kernel.  The reference ships no
+ * golden vector or known-answer test for this path, so the pin is the
+ * reference's search sources themselves (src/search_gpu.cu, src/utils.cu,
+ * src/uni.cpp, src/fileout.cpp), compiled unmodified for sm_100a by
+ * oracle/Makefile (target ref_gpu) and run on a B200: this file's ids, distance
+ * bits and hop counts equal that kernel's on every case of
+ * tests/test_gpu_ref_pin.py, and the kernel's outputs are committed as
+ * tests/golden/ref_kernel_small.npz, which tests/test_oracle.py checks on CPU.
+ * Where the reference kernel leaves an outcome to thread arrival order (equal
+ * distances at the cut, src/search_gpu.cu:530-532) the lowest id wins here.
+ * Only tests, the smoke check and the benchmark's checker may load this file.
  *
  * Semantics restated (per query):
  *   beam <- the M entry points (duplicates kept, as src/search_gpu.cu:392-407
