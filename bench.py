@@ -193,9 +193,10 @@ def reference_gpu_kernel(ix, base_h, adj_h, start_h, queries_h, gt_h, L, k, metr
         if int(np.abs(st[:, 0]).max()) != 0:
             return {"value": None, "unit": "queries/s", "sample": "skipped: a query of the sample did not fill its beam"}
         best, ids = None, None
-        for _ in range(2):
-            ids, _, hops, secs = oracle.ref_gpu_search(base_h, adj_h, start_h, queries_h, L, k, metric, max_degree=max_degree)
-            best = secs if best is None else min(best, secs)
+        with oracle.RefGpuIndex(base_h, adj_h, start_h, metric, max_degree=max_degree) as ref:
+            for _ in range(2):
+                ids, _, hops, secs = ref.search(queries_h, L, k)
+                best = secs if best is None else min(best, secs)
         m = min(len(queries_h), len(gt_h))
         return {"value": len(queries_h) / best, "unit": "queries/s", "L": L, "recall": oracle.recall(ids[:m], gt_h[:m], k),
                 "seconds": best, "hops": hops,
@@ -296,6 +297,9 @@ def run_latency(args, w, ix, ds, device, rank):
         return table
 
     table = measure()
+    ref_latency = None
+    if rank == 0 and not args.no_cpu_baseline:
+        ref_latency = reference_gpu_latency(ix, ds, w, L, k, cfg)
     # Second leg: 10 % of the points deleted with topology repair, then 5 % new points inserted with
     # neighbours from the same search kernel at L = 128 (src/index_gpu.cpp:138-224), then the same batches.
     n, extra = w["n"], w["n"] // 20
@@ -329,6 +333,7 @@ def run_latency(args, w, ix, ds, device, rank):
                "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                "config": {"workload": args.workload, "n": w["n"], "dim": dim, "metric": cfg["kind"], "max_degree": cfg["deg"],
                           "k": k, "L": L, "recall": recall, "batch_sizes": w["latency"], "latency": table,
+                          "reference_gpu_kernel_latency": ref_latency,
                           "after_10pct_delete_with_repair_and_5pct_insert": {
                               "latency": table_deleted, "recall": recall_deleted, "delete_s": round(t_del, 1),
                               "insert_s": round(t_ins, 1), "insert_batch": 32768,
@@ -338,6 +343,35 @@ def run_latency(args, w, ix, ds, device, rank):
                        "d2h_bytes_per_step": k * 4 * w["latency"][0] + 32},
                "gpu_launches": int(ix.launch_count - launches0)}
         print(json.dumps(out), flush=True)
+
+
+def reference_gpu_latency(ix, ds, w, L, k, cfg, batches=10):
+    """p50 of the reference's own search kernel (oracle/_ref, its sources compiled unmodified) per batch
+    size on the same index, entry points and queries: the reference's timed window, queries and results
+    on the device.  None when that build is absent; batches whose queries do not all fill their beam
+    are skipped (the reference kernel reads out of range for those)."""
+    from oracle import oracle
+    if not oracle.have_ref_gpu():
+        return None
+    try:
+        out = {}
+        with oracle.RefGpuIndex(ds.base.cpu().numpy(), ix.get_adjacency(), ix.get_start_ids(), cfg["kind"],
+                                max_degree=cfg["deg"]) as ref:
+            for B in w["latency"]:
+                us = []
+                for i in range(batches + 2):
+                    s0 = (i * B) % (w["q"] - B + 1)
+                    q = ds.test[s0:s0 + B].cpu().numpy()
+                    _, _, st, _ = ix.search(q, L, k, dists=False, stats=True)
+                    if int(np.abs(st[:, 0]).max()) != 0:
+                        continue
+                    _, _, _, secs = ref.search(q, L, k)
+                    if i >= 2:
+                        us.append(secs * 1e6)
+                out[B] = {"p50_us": float(np.percentile(us, 50)), "batches": len(us)} if us else None
+        return out
+    except Exception as e:
+        return {"failed": str(e)}
 
 
 def quick_workload(name, local, steps=3, warmup=2):

@@ -49,7 +49,8 @@ struct Options {
     int visit_cache_bits = 0;  // shared-memory cache of recently seen ids in front of the visited table (log2 entries)
     int sort_tile = 0;     // candidate sort tile in keys: 0 = automatic (about twice the beam capacity)
     int probe_carry = 1;   // carry ids the first probe pair leaves open into the next scout step (0 = settle them at once)
-    int gather = 0;        // row chunks to shared memory: 0 = one bulk copy per row chunk, 1 = 16-byte unit copies
+    int gather = -1;       // row chunks to shared memory: 0 = one bulk copy per row chunk, 1 = 16-byte unit copies,
+                           // 2 = tensor copies gathering four rows each, -1 = automatic (2 when the driver encodes tensor maps)
     int schedule = 0;      // order large batches for L2 locality: 0 = automatic (batches >= 8192), 1 = always, -1 = never
     int schedule_tc = 1;   // scheduling keys on the tensor cores (1) or by the fp32 SIMT tile kernel (0)
     int dense_passes = 3;  // tf32 passes of the dense scans behind coral_exact_knn: 3 = fp32-grade, 1 = plain tf32
@@ -174,7 +175,7 @@ coral::PlanOptions plan_options(const Options& o) {
     p.visit_cache_bits = o.visit_cache_bits;
     p.sort_tile = o.sort_tile;
     p.probe_carry = o.probe_carry;
-    p.gather = o.gather;
+    p.gather = o.gather < 0 ? (coral::row_gather_available() ? 2 : 0) : o.gather;
     return p;
 }
 
@@ -608,7 +609,7 @@ int coral_get_option(coral_index_t* h, const char* name, int* value) {
     else if (s == "cluster_size") *value = o.cluster_size;
     else if (s == "last_cluster_size") *value = h->last_cluster_size;
     else if (s == "schedule") *value = o.schedule;
-    else if (s == "gather") *value = o.gather;
+    else if (s == "gather") *value = o.gather < 0 ? (coral::row_gather_available() ? 2 : 0) : o.gather;
     else if (s == "probe_carry") *value = o.probe_carry;
     else if (s == "dense_passes") *value = o.dense_passes;
     else if (s == "schedule_tc") *value = o.schedule_tc;
@@ -840,7 +841,14 @@ static int enqueue_search(coral_index* h, const float* d_queries, int Q, int L, 
             h->last_scheduled = 1;
         }
     }
-    CK(coral::launch_beam_search(a, h->metric, grid, st, cs));
+    alignas(64) CUtensorMap row_map;
+    const CUtensorMap* row_map_ptr = nullptr;
+    if (p.gather == 2) {
+        if (!coral::make_row_gather_map(&row_map, h->d_vecs, h->n, h->dim, p.chunk_bytes / 4))
+            return fail(h, CORAL_ERR_CUDA, "could not encode the tensor map of the row array (gather = 2)");
+        row_map_ptr = &row_map;
+    }
+    CK(coral::launch_beam_search(a, h->metric, grid, st, cs, row_map_ptr));
     h->launches += 1;
     h->epoch_base += (uint32_t)Q;
     CK(cudaMemcpyAsync(h->h_ctrl, h->d_ctrl, kCtrlWords * sizeof(unsigned long long), cudaMemcpyDeviceToHost, st));
@@ -1012,10 +1020,21 @@ static int exact_knn_over(coral_index* h, const float* d_rows, int64_t n_rows, c
             qsrc = dq;
         }
         if (e == cudaSuccess) e = coral::dense_begin(w, qsrc, nq, h->dim, st, &h->launches);
-        for (int64_t r0 = 0; r0 < n_rows && e == cudaSuccess; r0 += b_cap) {
-            const int nr = (int)std::min<int64_t>(b_cap, n_rows - r0);
+        // The first rows of a query block are scanned in two short launches before the full-length
+        // ones.  While the per-row thresholds are still loose the epilogue's work differs from CTA to
+        // CTA; on a long launch the CTAs drift apart until they no longer share operand tiles in L2
+        // and each reads the rows from DRAM.  A launch boundary lines them up again, and after some
+        // 10^5 rows almost no column passes a threshold any more.
+        int64_t warm = 16384;
+        for (int64_t r0 = 0; r0 < n_rows && e == cudaSuccess;) {
+            int nr = (int)std::min<int64_t>(b_cap, n_rows - r0);
+            if (r0 < 16384 * 9 && (int64_t)nr > 2 * warm) {
+                nr = (int)warm;
+                warm *= 8;
+            }
             e = coral::dense_scan_chunk(w, qsrc, nq, d_rows + (size_t)r0 * h->dim, r0, nr, h->dim, h->metric, passes, keep,
                                         h->sm_count, st, &h->launches);
+            r0 += nr;
         }
         int32_t* io = i_dev ? ids_out + (size_t)q0 * k : di;
         float* dox = dists_out ? (d_dev ? dists_out + (size_t)q0 * k : dd) : nullptr;

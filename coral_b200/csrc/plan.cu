@@ -69,11 +69,29 @@ bool make_plan_warps(int dim, int smem_optin, const PlanOptions& o, int L, int w
     p.n_chunks = nc;
     p.chunk_bytes = row_bytes / nc;
     p.row_stride = p.chunk_bytes + (((p.chunk_bytes / 16) % 2 == 0) ? 16 : 0);
+    p.group_stride = 4 * p.row_stride;
+    p.tail_vec = p.chunk_bytes / 16;
     p.stage_bytes = 32 * p.row_stride;
+    if (o.gather == 2) {
+        // One tensor copy lands the chunks of four rows back to back, and its destination has to be
+        // 128-byte aligned, so the padding that keeps lane-per-row reads off the same banks goes
+        // into the chunk width itself: an odd number of 16-byte units (rows r and r + 1 of a group
+        // then start one bank group apart; lanes four apart still share one, a 2-way conflict).
+        // The chunks need not tile the row: the last one runs past its end and reads zeros there.
+        int units = imax(1, target / 16);
+        if (units % 2 == 0) ++units;
+        units = imin(units, 63);                 // a box is at most 256 elements wide
+        p.chunk_bytes = units * 16;
+        p.n_chunks = (row_bytes + p.chunk_bytes - 1) / p.chunk_bytes;
+        p.row_stride = p.chunk_bytes;
+        p.group_stride = align_up(4 * p.chunk_bytes, 128);
+        p.tail_vec = (row_bytes - (p.n_chunks - 1) * p.chunk_bytes) / 16;
+        p.stage_bytes = 8 * p.group_stride;
+    }
     p.LP = next_pow2(imax(L, 32));
     p.hs_bits = imin(imax(o.smem_hash_bits, 0), 16);
     p.vc_bits = imin(imax(o.visit_cache_bits, 0), 14);
-    p.gather = o.gather == 1 ? 1 : 0;
+    p.gather = (o.gather == 1 || o.gather == 2) ? o.gather : 0;
     p.carry = o.probe_carry != 0 ? 1 : 0;
 
     const int budget = smem_optin / p.ctas_per_sm - 1024;  // the runtime keeps 1 KB per CTA

@@ -33,6 +33,7 @@
 // no CTA (or cluster) takes another query.
 #include "search_kernel.cuh"
 
+#include <cstring>
 #include <mutex>
 
 namespace coral {
@@ -138,6 +139,17 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                      smem_u32(dst)),
                  "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
+}
+// Tensor copy that gathers one box (one row by chunk width) from each of four rows of a
+// two-dimensional tensor map and lands them back to back at dst (128-byte aligned); the box bytes
+// of all four rows, zero fill included, count on the mbarrier.
+__device__ __forceinline__ void tensor_gather4(void* dst, const CUtensorMap* map, int col, int r0, int r1, int r2, int r3,
+                                               uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(smem_u32(bar))
+        : "memory");
 }
 // 16-byte asynchronous copy global -> shared through the load/store path (L2 only, no L1
 // allocation); completion is tracked per thread in commit groups.
@@ -341,7 +353,7 @@ __device__ __forceinline__ float seed_distance(const float* __restrict__ row, co
 // merges; every CTA runs the scout/gather/distance pipeline against the shared global visited
 // table, work counter and candidate buffer; two cluster barriers per round.
 template <int METRIC, bool CLUSTER>
-__global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
+__global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a, const __grid_constant__ CUtensorMap row_map) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ Control S;
 
@@ -408,6 +420,10 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
     // walk the (row, unit) pairs of a stage 32 at a time, so one instruction copies whole
     // contiguous runs (two 256-byte chunks, one 512-byte chunk, ...).
     const bool unit_gather = P.gather == 1;
+    // Tensor gather (P.gather == 2): lane g < 8 copies the chunk of rows 4g..4g+3 with one
+    // instruction; row r of the stage then sits at (r / 4) * group_stride + (r % 4) * chunk_bytes.
+    const bool tensor_gather = P.gather == 2;
+    const int lane_row_off = tensor_gather ? (lane >> 2) * P.group_stride + (lane & 3) * P.chunk_bytes : lane * P.row_stride;
     const int lane_r0 = lane / chunk_vec, lane_u0 = lane % chunk_vec;
     const int step_r = 32 / chunk_vec, step_u = 32 % chunk_vec;
 
@@ -564,6 +580,22 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
                                 }
                             }
                             ldgsts_commit();
+                        } else if (tensor_gather) {
+                            const int groups = (cnt + 3) >> 2;
+                            if (lane == 0) mbar_expect_tx(&bars[st], (uint32_t)groups * 4u * (uint32_t)P.chunk_bytes);
+                            __syncwarp();
+                            if (lane < groups) {
+                                // a group the batch does not fill repeats its first row
+                                const int* ids = bids + (b & 1u) * 32 + lane * 4;
+                                int r[4];
+#pragma unroll
+                                for (int t = 0; t < 4; ++t) {
+                                    r[t] = lane * 4 + t < cnt ? ids[t] : ids[0];
+                                    if (!CORAL_CHECK(r[t] >= 0 && (int64_t)r[t] < a.n && cnt <= 32 && (int)st < P.stages, 3, r[t], cnt)) r[t] = 0;
+                                }
+                                tensor_gather4(stage0 + (size_t)st * P.stage_bytes + (size_t)lane * P.group_stride, &row_map,
+                                               c * chunk_floats, r[0], r[1], r[2], r[3], &bars[st]);
+                            }
                         } else {
                             if (lane == 0) mbar_expect_tx(&bars[st], (uint32_t)cnt * (uint32_t)P.chunk_bytes);
                             __syncwarp();
@@ -759,9 +791,9 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a) {
                         if (lane < cnt)
                             acc = accumulate_chunk<METRIC>(
                                 acc,
-                                reinterpret_cast<const float4*>(stage0 + (size_t)st * P.stage_bytes +
-                                                                (size_t)lane * P.row_stride),
-                                reinterpret_cast<const float4*>(sq + (size_t)c * chunk_floats), chunk_vec);
+                                reinterpret_cast<const float4*>(stage0 + (size_t)st * P.stage_bytes + (size_t)lane_row_off),
+                                reinterpret_cast<const float4*>(sq + (size_t)c * chunk_floats),
+                                c + 1 == n_chunks ? P.tail_vec : chunk_vec);
                         fence_async_smem();
                         __syncwarp();
                         --inflight;
@@ -1029,13 +1061,58 @@ bool grant_smem(int metric, bool cluster, int bytes) {
 }
 }  // namespace
 
-cudaError_t launch_beam_search(const SearchArgs& a, int metric, int grid, cudaStream_t stream, int cluster_size) {
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn tensor_map_encoder() {
+    static std::mutex mu;
+    static EncodeTiledFn enc = nullptr;
+    static bool asked = false;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!asked) {
+        asked = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            enc = reinterpret_cast<EncodeTiledFn>(p);
+        else
+            cudaGetLastError();
+    }
+    return enc;
+}
+}  // namespace
+
+bool row_gather_available() { return tensor_map_encoder() != nullptr; }
+
+bool make_row_gather_map(CUtensorMap* map, const float* vecs, int64_t n, int dim, int box_floats) {
+    EncodeTiledFn enc = tensor_map_encoder();
+    if (!enc) return false;
+    if (!vecs || n <= 0 || dim <= 0 || dim % 4 != 0 || box_floats <= 0 || box_floats > 256 || box_floats % 4 != 0 ||
+        ((uintptr_t)vecs & 15u) != 0)
+        return false;
+    const cuuint64_t gdim[2] = {(cuuint64_t)dim, (cuuint64_t)n};
+    const cuuint64_t gstride[1] = {(cuuint64_t)dim * 4};
+    const cuuint32_t box[2] = {(cuuint32_t)box_floats, 1};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(vecs), gdim, gstride, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+cudaError_t launch_beam_search(const SearchArgs& a, int metric, int grid, cudaStream_t stream, int cluster_size,
+                               const CUtensorMap* row_map) {
     const int threads = a.plan.warps * 32;
+    if (a.plan.gather == 2 && !row_map) return cudaErrorInvalidValue;
+    alignas(64) CUtensorMap map;
+    if (row_map) map = *row_map;
+    else memset(&map, 0, sizeof map);   // never dereferenced in the other gather modes
     if (cluster_size <= 1) {
         if (metric == 0)
-            beam_search_kernel<0, false><<<grid, threads, a.plan.smem_bytes, stream>>>(a);
+            beam_search_kernel<0, false><<<grid, threads, a.plan.smem_bytes, stream>>>(a, map);
         else
-            beam_search_kernel<1, false><<<grid, threads, a.plan.smem_bytes, stream>>>(a);
+            beam_search_kernel<1, false><<<grid, threads, a.plan.smem_bytes, stream>>>(a, map);
         return cudaGetLastError();
     }
     cudaLaunchConfig_t cfg = {};
@@ -1050,8 +1127,8 @@ cudaError_t launch_beam_search(const SearchArgs& a, int metric, int grid, cudaSt
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (metric == 0) return cudaLaunchKernelEx(&cfg, beam_search_kernel<0, true>, a);
-    return cudaLaunchKernelEx(&cfg, beam_search_kernel<1, true>, a);
+    if (metric == 0) return cudaLaunchKernelEx(&cfg, beam_search_kernel<0, true>, a, map);
+    return cudaLaunchKernelEx(&cfg, beam_search_kernel<1, true>, a, map);
 }
 
 int beam_search_occupancy(const SearchPlan& p, int metric) {

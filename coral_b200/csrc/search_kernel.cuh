@@ -1,5 +1,6 @@
 // Host/device shared declarations of the beam-search kernel (sm_100a).
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -15,15 +16,18 @@ struct SearchPlan {
     int warps;        // warps per CTA; every warp runs its own gather/distance pipeline
     int stages;       // per-warp ring depth (stages of 32 row chunks)
     int chunk_bytes;  // bytes of one row chunk moved by one bulk copy (multiple of 16)
-    int n_chunks;     // chunks per row (chunk_bytes * n_chunks == dim * 4)
+    int n_chunks;     // chunks per row (chunk_bytes * n_chunks == dim * 4; >= dim * 4 in gather mode 2)
     int row_stride;   // bytes between two rows inside a stage (padded against bank conflicts)
-    int stage_bytes;  // 32 * row_stride
+    int group_stride; // gather mode 2: bytes between two groups of four rows (multiple of 128)
+    int tail_vec;     // 16-byte units of the last chunk that belong to the row (the rest reads as zeros)
+    int stage_bytes;  // 32 * row_stride (8 * group_stride in gather mode 2)
     int hs_bits;      // log2 entries of the shared-memory visited hash, 0 = none
     int vc_bits;      // log2 entries of the shared-memory cache of recently seen ids, 0 = none
     int LP;           // beam array length: L rounded up to a power of two
     int tile_max;     // largest candidate tile sorted at once (power of two)
     int ctas_per_sm;
-    int gather;       // how row chunks reach shared memory: 0 = one bulk copy per row chunk, 1 = 16-byte unit copies
+    int gather;       // how row chunks reach shared memory: 0 = one bulk copy per row chunk, 1 = 16-byte unit copies,
+                      // 2 = tensor copies that gather the chunks of four rows each (needs the row map)
     int carry;        // 1 = an id its first probe pair does not settle is carried into the lane's next scout step
     int off_query, off_beam0, off_beam1, off_exp, off_hash, off_vcache, off_bar, off_pend, off_bids, off_stage;
     int smem_bytes;
@@ -76,7 +80,15 @@ int* granted_slot(int* table, int device, int metric, bool cluster);
 // Launches the kernel for `metric` (0 = L2, 1 = IP) with `grid` CTAs on `stream`.  With
 // cluster_size > 1 the grid is made of thread-block clusters of that many CTAs, each cluster
 // working on one query at a time (grid must be a multiple of cluster_size).
-cudaError_t launch_beam_search(const SearchArgs& a, int metric, int grid, cudaStream_t stream, int cluster_size = 1);
+// `row_map` (gather mode 2 only): the tensor map made by make_row_gather_map for a.vecs and this plan.
+cudaError_t launch_beam_search(const SearchArgs& a, int metric, int grid, cudaStream_t stream, int cluster_size = 1,
+                               const CUtensorMap* row_map = nullptr);
+// Tensor map of the [n][dim] fp32 row array for gather mode 2: two dimensions, a box of one row by
+// `box_floats` columns, no swizzle; columns past `dim` read as zeros.  False when the driver's
+// encoder is not available or refuses the shape.
+bool make_row_gather_map(CUtensorMap* map, const float* vecs, int64_t n, int dim, int box_floats);
+// Whether the driver's tensor-map encoder can be reached at all (asked once per process).
+bool row_gather_available();
 // Registers the dynamic shared-memory size with the runtime and returns the
 // number of CTAs of this plan that fit one SM (0 on failure).
 int beam_search_occupancy(const SearchPlan& p, int metric);

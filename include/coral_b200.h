@@ -181,7 +181,11 @@ int64_t coral_launch_count(coral_index_t* h);
  *                            512 when the row does not split into 256-byte chunks and five CTAs
  *                            still fit an SM)
  *   "stages"                 stage buffers per warp; 0 = automatic (1)
- *   "gather"                 0 = one bulk copy per row chunk (default), 1 = 16-byte cp.async units
+ *   "gather"                 how row chunks reach shared memory: 0 = one bulk copy per row chunk,
+ *                            1 = 16-byte cp.async units, 2 = one tensor copy per four rows (a tensor map
+ *                            of the row array, chunk width an odd number of 16-byte units, 272 bytes
+ *                            unless "chunk_bytes" says otherwise); -1 = automatic (default): 2 when the
+ *                            driver's tensor-map encoder is available, else 0
  *   "smem_hash_bits"         log2 entries of a shared-memory visited table in front of the global
  *                            one; 0 = none (default)
  *   "visit_cache_bits"       log2 entries of a shared-memory cache of recently seen ids; 0 = none

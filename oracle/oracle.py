@@ -418,35 +418,67 @@ def have_ref_gpu() -> bool:
     return os.path.exists(os.path.join(_HERE, "_ref", "libref_gpu.so"))
 
 
-def ref_gpu_search(base, adj, start_ids, queries, L, k, metric, max_degree=None):
-    """The reference's own GPUFuncs::search_gpu + beam_search_kernel (bitset overload) on the
-    current CUDA device.  Every query must fill its beam (oracle status 0): the reference
-    kernel reads out of range otherwise.  Returns (ids, dists, total_hops, seconds)."""
+def _ref_gpu_lib():
     global _ref_gpu
     if _ref_gpu is None:
         _ref_gpu = C.CDLL(os.path.join(_HERE, "_ref", "libref_gpu.so"))
         f32p, i32p = C.POINTER(C.c_float), C.POINTER(C.c_int32)
-        _ref_gpu.coral_ref_gpu_search.restype = C.c_int
-        _ref_gpu.coral_ref_gpu_search.argtypes = [
-            f32p, C.c_int64, C.c_int, i32p, C.c_int, C.c_int, C.c_int, i32p, C.c_int, f32p, C.c_int,
-            C.c_int, C.c_int, i32p, f32p, C.POINTER(C.c_int64), C.POINTER(C.c_double)]
-    base, bp = _f32(base)
-    adj, ap = _i32(adj)
-    start_ids, sp = _i32(start_ids)
-    queries, qp = _f32(queries)
-    n, dim = base.shape
-    Q = queries.shape[0]
-    if max_degree is None:
-        max_degree = int((adj >= 0).sum(1).max())
-    ids = np.empty((Q, k), np.int32)
-    dists = np.empty((Q, k), np.float32)
-    hops = C.c_int64(0)
-    secs = C.c_double(0.0)
-    rc = _ref_gpu.coral_ref_gpu_search(bp, n, dim, ap, adj.shape[1], max_degree, metric_id(metric), sp,
-                                       len(start_ids), qp, Q, L, k,
-                                       ids.ctypes.data_as(C.POINTER(C.c_int32)),
-                                       dists.ctypes.data_as(C.POINTER(C.c_float)),
-                                       C.byref(hops), C.byref(secs))
-    if rc != 0:
-        raise RuntimeError(f"coral_ref_gpu_search failed with {rc}")
-    return ids, dists, int(hops.value), float(secs.value)
+        _ref_gpu.coral_ref_gpu_open.restype = C.c_void_p
+        _ref_gpu.coral_ref_gpu_open.argtypes = [f32p, C.c_int64, C.c_int, i32p, C.c_int, C.c_int, C.c_int, i32p, C.c_int]
+        _ref_gpu.coral_ref_gpu_close.restype = None
+        _ref_gpu.coral_ref_gpu_close.argtypes = [C.c_void_p]
+        _ref_gpu.coral_ref_gpu_run.restype = C.c_int
+        _ref_gpu.coral_ref_gpu_run.argtypes = [C.c_void_p, f32p, C.c_int, C.c_int, C.c_int, i32p, f32p,
+                                               C.POINTER(C.c_int64), C.POINTER(C.c_double)]
+    return _ref_gpu
+
+
+class RefGpuIndex:
+    """The reference's device-side index (Slot records + row array) on the current CUDA device, for
+    repeated calls of the reference's own GPUFuncs::search_gpu + beam_search_kernel (bitset
+    overload).  Every query must fill its beam (oracle status 0): the reference kernel reads out of
+    range otherwise."""
+
+    def __init__(self, base, adj, start_ids, metric, max_degree=None):
+        lib = _ref_gpu_lib()
+        base, bp = _f32(base)
+        adj, ap = _i32(adj)
+        start_ids, sp = _i32(start_ids)
+        n, dim = base.shape
+        if max_degree is None:
+            max_degree = int((adj >= 0).sum(1).max())
+        self.dim = dim
+        self._h = lib.coral_ref_gpu_open(bp, n, dim, ap, adj.shape[1], max_degree, metric_id(metric), sp, len(start_ids))
+        if not self._h:
+            raise RuntimeError("coral_ref_gpu_open failed")
+
+    def search(self, queries, L, k):
+        """Returns (ids, dists, total_hops, seconds of the reference's own timed window)."""
+        queries, qp = _f32(queries)
+        Q = queries.shape[0]
+        ids = np.empty((Q, k), np.int32)
+        dists = np.empty((Q, k), np.float32)
+        hops = C.c_int64(0)
+        secs = C.c_double(0.0)
+        rc = _ref_gpu_lib().coral_ref_gpu_run(self._h, qp, Q, L, k, ids.ctypes.data_as(C.POINTER(C.c_int32)),
+                                              dists.ctypes.data_as(C.POINTER(C.c_float)), C.byref(hops), C.byref(secs))
+        if rc != 0:
+            raise RuntimeError(f"coral_ref_gpu_run failed with {rc}")
+        return ids, dists, int(hops.value), float(secs.value)
+
+    def close(self):
+        if self._h:
+            _ref_gpu_lib().coral_ref_gpu_close(self._h)
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
+def ref_gpu_search(base, adj, start_ids, queries, L, k, metric, max_degree=None):
+    """One search through a temporary RefGpuIndex.  Returns (ids, dists, total_hops, seconds)."""
+    with RefGpuIndex(base, adj, start_ids, metric, max_degree) as r:
+        return r.search(queries, L, k)

@@ -105,6 +105,9 @@ def test_underfull_beam_is_reported_not_faulted():
     {"gather": 1, "stages": 3, "chunk_bytes": 128, "warps": 3},
     {"gather": 1, "chunk_bytes": 1024, "warps": 2, "ctas_per_sm": 1},   # more units per chunk than lanes
     {"gather": 0, "stages": 2},
+    {"gather": 2},                                 # tensor copies that gather four rows each
+    {"gather": 2, "chunk_bytes": 48, "stages": 3, "warps": 3},
+    {"gather": 2, "chunk_bytes": 1008, "warps": 2, "ctas_per_sm": 1},   # the widest box: 63 units
     {"probe_carry": 0},                            # ids the first probe pair leaves open are settled at once
     {"probe_carry": 1, "ghash_entries": 4096},     # a crowded visited table: many carried probes
 ])
@@ -130,6 +133,25 @@ def test_locality_scheduling_changes_only_the_order_of_work(metric):
     r = cases.random_case(metric, 3000, 36, 32, 50, m=3, seed=41)             # tiny frontier, odd dim
     with make_index(r, 50, 64, 10, options={"schedule": 1}) as ix:
         assert_same(r, ix, 64, 10, modes=(1,))
+
+
+@pytest.mark.parametrize("metric", ["l2", "ip"])
+def test_tensor_gather_of_rows(metric):
+    # gather = 2 moves the chunks of four rows with one tensor copy; the last chunk of a row runs
+    # past its end (zero fill).  Rows of 144, 800 and 2048 bytes, batches that do not fill a group
+    # of four, large batches and clusters that share a query.
+    c = cases.structured(metric)
+    with make_index(c, len(c.queries), 128, 10, options={"gather": 2}) as ix:
+        assert ix.get_option("plan_chunk_bytes") % 32 == 16
+        assert_same(c, ix, 64, 10)
+        assert_same(c, ix, 128, 10, queries=c.queries[:3], modes=(0,))       # cluster mode
+        assert ix.get_option("last_cluster_size") >= 2
+    for dim, deg in ((36, 32), (200, 32), (512, 64)):
+        r = cases.random_case(metric, 3000, dim, deg, 40, m=5, seed=dim)
+        for opts in ({"gather": 2}, {"gather": 2, "chunk_bytes": 400, "stages": 2}):
+            with make_index(r, 40, 64, 10, options=opts) as ix:
+                assert_same(r, ix, 64, 10)
+                assert_same(r, ix, 33, 7, queries=r.queries[:9])
 
 
 def test_small_sort_tiles_take_many_fill_passes():
