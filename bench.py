@@ -185,6 +185,7 @@ def reference_gpu_kernel(ix, base_h, adj_h, start_h, queries_h, gt_h, L, k, metr
     (src/search_gpu.cu:861-877).  Reported beside the CPU baseline; None when that build is absent.
     The reference kernel reads out of range for a query whose beam never fills, so it only runs after
     this library's search reported status 0 for every query of the sample."""
+    import numpy as np
     from oracle import oracle
     if not oracle.have_ref_gpu():
         return None
@@ -350,6 +351,7 @@ def reference_gpu_latency(ix, ds, w, L, k, cfg, batches=10):
     size on the same index, entry points and queries: the reference's timed window, queries and results
     on the device.  None when that build is absent; batches whose queries do not all fill their beam
     are skipped (the reference kernel reads out of range for those)."""
+    import numpy as np
     from oracle import oracle
     if not oracle.have_ref_gpu():
         return None
