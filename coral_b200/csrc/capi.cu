@@ -1020,18 +1020,15 @@ static int exact_knn_over(coral_index* h, const float* d_rows, int64_t n_rows, c
             qsrc = dq;
         }
         if (e == cudaSuccess) e = coral::dense_begin(w, qsrc, nq, h->dim, st, &h->launches);
-        // The first rows of a query block are scanned in two short launches before the full-length
-        // ones.  While the per-row thresholds are still loose the epilogue's work differs from CTA to
-        // CTA; on a long launch the CTAs drift apart until they no longer share operand tiles in L2
-        // and each reads the rows from DRAM.  A launch boundary lines them up again, and after some
-        // 10^5 rows almost no column passes a threshold any more.
-        int64_t warm = 16384;
+        // Rows are scanned in launches of at most 131072 (the first of a query block 16384).  The
+        // epilogue's work differs from CTA to CTA while the per-row thresholds are loose; on a long
+        // launch the CTAs drift apart until they no longer share operand tiles in L2 and each reads
+        // the rows from DRAM (measured: 235 GB of DRAM reads for a 2 GB operand, half speed).  A
+        // launch boundary lines them up again and costs microseconds.
         for (int64_t r0 = 0; r0 < n_rows && e == cudaSuccess;) {
             int nr = (int)std::min<int64_t>(b_cap, n_rows - r0);
-            if (r0 < 16384 * 9 && (int64_t)nr > 2 * warm) {
-                nr = (int)warm;
-                warm *= 8;
-            }
+            const int cap = r0 == 0 ? 16384 : 131072;
+            if (nr > cap + cap / 2) nr = cap;
             e = coral::dense_scan_chunk(w, qsrc, nq, d_rows + (size_t)r0 * h->dim, r0, nr, h->dim, h->metric, passes, keep,
                                         h->sm_count, st, &h->launches);
             r0 += nr;
