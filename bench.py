@@ -64,9 +64,11 @@ def metric_name(workload, w):
     return (f"QPS @ recall@{w['k']}>=0.95, {size}x{cfg['dim']} {cfg['kind'].upper()}"
             + (" per shard, sharded" if w.get("sharded") else ""))
 PEAK_FALLBACK_GBS = 6650.0
-# DRAM bytes per algorithmic byte of the search kernel, from the ncu captures summarised under
-# profiles/ (a profile constant, not a measurement of this run): workload -> ratio.
-DRAM_PER_ALGORITHMIC_BYTE = {"small": 0.73}
+# DRAM bytes per algorithmic byte of the search kernel, from the ncu capture of the 1M x 512 case
+# summarised under profiles/ (a profile constant, not a measurement of this run): workload -> ratio.
+# The 10M x 512 workloads use the same ratio: with a 23 GB index L2 serves less of the gather than
+# with 2.3 GB, so for them the figure is a lower bound of the DRAM share.
+DRAM_PER_ALGORITHMIC_BYTE = {"small": 0.743, "c3": 0.743}
 
 
 def log(*a):
@@ -743,8 +745,10 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_kind,
                          "traffic": (ratio * alg_bytes if ratio and world == 1 else None),
-                         "traffic_source": ("profile constant: DRAM bytes per algorithmic byte from the ncu capture "
-                                            "summarised in profiles/, scaled to this launch" if ratio else None),
+                         "traffic_source": (("profile constant: 0.743 DRAM bytes per algorithmic byte in the ncu capture of the "
+                                             "1M x 512 case (profiles/), scaled to this launch by its algorithmic bytes"
+                                             + ("; a lower bound at 10M, where L2 serves less" if w["n"] > 1_000_000 else ""))
+                                            if ratio else None),
                          "dram_frac": (ratio * achieved / peak if ratio else None),
                          "algorithmic_bytes_per_step": total_alg, "kernel": "beam_search_kernel",
                          "note": "per GPU (slowest rank); frac = ALGORITHMIC bytes (n_dist*dim*4 + n_exp*deg_pad*4 + dim*4 "
