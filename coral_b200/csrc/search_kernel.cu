@@ -526,7 +526,35 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a, const __g
             {
                 int pend_n = 0;
                 int bcnt0 = 0, bcnt1 = 0;          // rows in batch slot 0 / 1
-                bool more = exp_count > 0;
+                // `more`: a step of the round's expansion list has been claimed for this warp and its
+                // neighbour ids are on their way (or already) in nv[]: the adjacency rows of a step are
+                // requested one step ahead, so their latency overlaps the visited-table probes of the
+                // step before instead of preceding its own.
+                bool more = false;
+                int nv[kIdsPerLane];
+                const int total_slots = exp_count << a.deg_shift;
+                auto claim_step = [&]() {
+                    int s0 = total_slots;
+                    if (lane == 0) s0 = atomicAdd(p_exp_next, step_slots);
+                    s0 = __shfl_sync(0xffffffffu, s0, 0);
+                    more = s0 < total_slots;
+                    if (more && lane == 0) {   // entries whose first slot falls into this step
+                        const int s1 = s0 + step_slots < total_slots ? s0 + step_slots : total_slots;
+                        n_exp += ((s1 + a.deg_pad - 1) >> a.deg_shift) - ((s0 + a.deg_pad - 1) >> a.deg_shift);
+                    }
+#pragma unroll
+                    for (int t = 0; t < kIdsPerLane; ++t) {
+                        const int slot = s0 + lane + 32 * t;
+                        const int ent = slot >> a.deg_shift;
+                        nv[t] = -1;
+                        if (more && t < ipl && ent < exp_count) {
+                            const int node = CLUSTER ? __ldcg(gexp + ent) : exp_list[ent];
+                            if (CORAL_CHECK(ent < a.L && node >= 0 && (int64_t)node < a.n, 4, node, ent))
+                                nv[t] = __ldg(a.adj + (size_t)node * a.deg_pad + (slot & (a.deg_pad - 1)));
+                        }
+                    }
+                };
+                if (exp_count > 0) claim_step();
                 float acc = 0.f;
                 // A scout step is split in two: its compare-and-swaps are issued and the warp goes back to
                 // gathering and distances; their answers (which take microseconds under load) are only
@@ -670,31 +698,10 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a, const __g
                     }
                     if ((more || has_carry) && !sc_pending && pend_n < kScoutAhead) {
                         // ---- scout, first half: adjacency rows of the next slots, visited-table probes
-                        int s0 = 0;
-                        const int total_slots = exp_count << a.deg_shift;
-                        if (more) {
-                            if (lane == 0) s0 = atomicAdd(p_exp_next, step_slots);
-                            s0 = __shfl_sync(0xffffffffu, s0, 0);
-                            if (s0 >= total_slots) {
-                                more = false;
-                                if (!has_carry) continue;
-                            } else if (lane == 0) {   // entries whose first slot falls into this step
-                                const int s1 = s0 + step_slots < total_slots ? s0 + step_slots : total_slots;
-                                n_exp += ((s1 + a.deg_pad - 1) >> a.deg_shift) - ((s0 + a.deg_pad - 1) >> a.deg_shift);
-                            }
-                        }
                         int v[kIdsPerLane];
 #pragma unroll
-                        for (int t = 0; t < kIdsPerLane; ++t) {
-                            const int slot = s0 + lane + 32 * t;
-                            const int ent = slot >> a.deg_shift;
-                            v[t] = -1;
-                            if (more && t < ipl && ent < exp_count) {
-                                const int node = CLUSTER ? __ldcg(gexp + ent) : exp_list[ent];
-                                if (CORAL_CHECK(ent < a.L && node >= 0 && (int64_t)node < a.n, 4, node, ent))
-                                    v[t] = __ldg(a.adj + (size_t)node * a.deg_pad + (slot & (a.deg_pad - 1)));
-                            }
-                        }
+                        for (int t = 0; t < kIdsPerLane; ++t) v[t] = more ? nv[t] : -1;
+                        if (more) claim_step();   // the next step's rows are requested before this step's probes
                         if (P.hs_bits == 0 && P.vc_bits == 0) {
                             // Visited set entirely in the global table.  The first probe slots of a lane's
                             // ids are loaded side by side; a slot of another query (or never used) is
