@@ -71,6 +71,28 @@ PEAK_FALLBACK_GBS = 6650.0
 DRAM_PER_ALGORITHMIC_BYTE = {"small": 0.743, "c3": 0.743}
 
 
+_RESULT_FD = None
+
+
+def claim_stdout():
+    """Keeps the process's standard output for the one result line: everything else that writes to
+    file descriptor 1 from here on (libraries such as NCCL print banners there) goes to stderr."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(obj):
+    line = (json.dumps(obj) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(line.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, line)
+
+
 def log(*a):
     print(*a, file=sys.stderr, flush=True)
 
@@ -215,8 +237,8 @@ def run_reference(args, w, rank, world):
         return
     import torch
     if not torch.cuda.is_available():
-        print(json.dumps({"impl": "reference", "unavailable": "the index for the CPU arm is built with the library's GPU "
-                          "builder; no CUDA device here"}), flush=True)
+        emit({"impl": "reference", "unavailable": "the index for the CPU arm is built with the library's GPU "
+              "builder; no CUDA device here"})
         return
     from coral_b200 import synth
     ds, ix, info = build_index(w, 0)
@@ -246,7 +268,7 @@ def run_reference(args, w, rank, world):
         "cpu_baseline": dict(r, value=qps),
         "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(out), flush=True)
+    emit(out)
 
 
 def run_latency(args, w, ix, ds, device, rank):
@@ -345,7 +367,7 @@ def run_latency(args, w, ix, ds, device, rank):
                "e2e": {"value": b1["e2e_p50_us"], "unit": "us", "h2d_bytes_per_step": dim * 4 * w["latency"][0],
                        "d2h_bytes_per_step": k * 4 * w["latency"][0] + 32},
                "gpu_launches": int(ix.launch_count - launches0)}
-        print(json.dumps(out), flush=True)
+        emit(out)
 
 
 def reference_gpu_latency(ix, ds, w, L, k, cfg, batches=10):
@@ -500,6 +522,7 @@ def main():
     ap.add_argument("--option", action="append", default=[], help="kernel tuning knob name=value")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
+    claim_stdout()
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -757,7 +780,7 @@ def main():
             "cpu_baseline": cpu,
             "clocks": clocks,
         }
-        print(json.dumps(out), flush=True)
+        emit(out)
     if comm is not None:
         comm.close()
     if world > 1:
