@@ -86,7 +86,19 @@ void IndexGPU::BuildGPU(size_t n_sq, float* sq_data, size_t n_bp, float* bp_data
     capacity_ = nd_;
     check(coral_index_set_vectors(handle_, h_base_), "coral_index_set_vectors");
     std::vector<int32_t> knn(n_sq * (size_t)k_);
-    check(coral_exact_knn(handle_, sq_data, (int)n_sq, k_, knn.data(), nullptr, nullptr), "coral_exact_knn");   // src/knn.cu:174-193
+    const std::string train_gt = parameters.Get<std::string>("train_gt_file", std::string(""));
+    if (!train_gt.empty() && train_gt != "None") {
+        // the training queries' k-NN lists come from a file instead of the search (src/index_gpu.cpp:505-515)
+        const coral_host::GroundTruth lists = coral_host::gt_load(train_gt);
+        if (lists.k != k_) throw std::runtime_error("train_gt_file: its k differs from the build's k");
+        if ((size_t)lists.nq < n_sq) throw std::runtime_error("train_gt_file: fewer lists than training queries");
+        for (size_t i = 0; i < knn.size(); ++i) {
+            knn[i] = lists.ids[i];
+            if (knn[i] < 0 || (size_t)knn[i] >= nd_) throw std::runtime_error("train_gt_file: id out of range");
+        }
+    } else {
+        check(coral_exact_knn(handle_, sq_data, (int)n_sq, k_, knn.data(), nullptr, nullptr), "coral_exact_knn");   // src/knn.cu:174-193
+    }
     check(coral_build_begin(handle_), "coral_build_begin");
     check(coral_build_nap(handle_, knn.data(), (int)n_sq, k_, PC.batch), "coral_build_nap");
     int64_t n_iso = 0;

@@ -263,3 +263,67 @@ def test_update_driver_slides_the_window_like_the_library_calls(tmp_path):
     st = np.empty(64, np.int32)
     m = host.coral_host_start_ids_load(str(tmp_path / "final" / "graph.search_start_ids").encode(), st.ctypes.data, 64)
     assert m == len(want_starts) and np.array_equal(st[:m], want_starts)
+
+
+@pytest.mark.parametrize("from_lists", [False, True])
+def test_build_driver_writes_the_graph_the_library_builds(tmp_path, from_lists):
+    """test_build_pipeline with the reference's flags: IndexGPU::BuildGPU over .fbin files writes a
+    graph directory that holds exactly the graph and entry points the same build gives through the
+    binding (held to the oracle in test_gpu_build.py), searchable by test_search_pipeline.  With
+    --train_gt_file the training queries' lists are read from a file instead of searched."""
+    import ctypes as C
+    from coral_b200 import capi, synth
+    build_host.build()
+    n, dim, deg, kb = 5000, 48, 32, 40
+    ds = synth.make_ip_cones(n, 1200, 50, dim=dim, clusters=8, seed=5, latent_dim=8, latent_jitter=0.5)
+    base, train, q = (np.ascontiguousarray(a.numpy()) for a in (ds.base, ds.train, ds.test))
+    for name, arr in (("base", base), ("train", train), ("query", q)):
+        (tmp_path / f"{name}.fbin").write_bytes(struct.pack("<ii", *arr.shape) + arr.tobytes())
+    # the driver unit-normalises what it loads; take the vectors back through the same loader so that the
+    # binding below sees the same bits
+    host = C.CDLL(build_host.HOST_LIB)
+    host.coral_host_fbin_load.argtypes = [C.c_char_p, C.c_void_p, C.c_int64, C.POINTER(C.c_int64), C.POINTER(C.c_int), C.c_int]
+    for name, arr in (("base", base), ("train", train), ("query", q)):
+        nn, dd = C.c_int64(0), C.c_int(0)
+        assert host.coral_host_fbin_load(str(tmp_path / f"{name}.fbin").encode(), arr.ctypes.data, arr.size, C.byref(nn),
+                                         C.byref(dd), 1) == 0 and (nn.value, dd.value) == arr.shape
+    gt, _ = oracle.exact_knn(base, q, 10, "ip")
+    (tmp_path / "gt.bin").write_bytes(struct.pack("<ii", *gt.shape) + gt.astype(np.int32).tobytes())
+    (tmp_path / "config.json").write_text('{"dim": %d, "k": %d, "batch": 256, "enhance_search_batch": 2048, '
+                                          '"enhance_nap_batch": 512, "test_beam_capacity": 64}' % (dim, kb))
+    lists, _ = oracle.exact_knn(base, train, kb, "ip")
+    extra = []
+    if from_lists:
+        # lists that the exact search would NOT give (each shifted by one rank): the driver must use them
+        wide, _ = oracle.exact_knn(base, train, kb + 1, "ip")
+        lists = np.ascontiguousarray(wide[:, 1:])
+        (tmp_path / "train_gt.bin").write_bytes(struct.pack("<ii", *lists.shape) + lists.astype(np.int32).tobytes())
+        extra = ["--train_gt_file", str(tmp_path / "train_gt.bin")]
+    exe = os.path.join(os.path.dirname(build_host.HOST_LIB), "test_build_pipeline")
+    cmd = [exe, "--data_type", "float", "--dist", "ip", "--dataset", "synthetic", "--base_data_path", str(tmp_path / "base.fbin"),
+           "--sampled_query_data_path", str(tmp_path / "train.fbin"), "--M_pjbp", str(deg), "--k", str(kb), "--CE", "1",
+           "--graph_path", str(tmp_path / "graph"), "--config_file", str(tmp_path / "config.json"),
+           "--query_test_file", str(tmp_path / "query.fbin"), "--gt_test_file", str(tmp_path / "gt.bin"), *extra]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    line = [ln for ln in r.stdout.splitlines() if ln.startswith("Search result: recall@10=")][-1]
+    assert float(line.split("=")[1].split(",")[0]) >= 0.9, line
+
+    with capi.Index(n, dim, deg, "ip") as ix:
+        ix.set_vectors(base)
+        ix.build_begin()
+        ix.build_nap(lists.astype(np.int32), 256)
+        n_iso = ix.build_connect_enhance(kb, 256, 2048, 512, 16)
+        assert n_iso > 0
+        ix.build_end()
+        want_adj, want_starts = ix.get_adjacency(), ix.get_start_ids()
+    host.coral_host_graph_dir_load.argtypes = [C.c_char_p, C.c_int64, C.c_int, C.c_void_p, C.POINTER(C.c_int)]
+    host.coral_host_start_ids_load.argtypes = [C.c_char_p, C.c_void_p, C.c_int]
+    got = np.empty((n, 128), np.int32)
+    dp = C.c_int(0)
+    assert host.coral_host_graph_dir_load(str(tmp_path / "graph").encode(), n, deg, got.ctypes.data, C.byref(dp)) == 0
+    got = got.reshape(-1)[: n * dp.value].reshape(n, dp.value)
+    assert dp.value == want_adj.shape[1] and np.array_equal(got, want_adj)
+    st = np.empty(64, np.int32)
+    m = host.coral_host_start_ids_load(str(tmp_path / "graph" / "graph.search_start_ids").encode(), st.ctypes.data, 64)
+    assert m == len(want_starts) and np.array_equal(st[:m], want_starts)
