@@ -533,13 +533,21 @@ __global__ void __maxnreg__(96) beam_search_kernel(const SearchArgs a, const __g
                 bool more = false;
                 int nv[kIdsPerLane];
                 const int total_slots = exp_count << a.deg_shift;
+                // The last steps of a round are claimed 32 slots at a time, so that the CTA's warps run out
+                // of work within a quarter of a step of each other instead of a whole one.
+                const int tail_slots = (nthreads >> 5) * step_slots;
                 auto claim_step = [&]() {
-                    int s0 = total_slots;
-                    if (lane == 0) s0 = atomicAdd(p_exp_next, step_slots);
+                    int s0 = total_slots, want = step_slots;
+                    if (lane == 0) {
+                        if (!CLUSTER && total_slots - *(volatile int*)p_exp_next <= tail_slots) want = 32;
+                        s0 = atomicAdd(p_exp_next, want);
+                    }
                     s0 = __shfl_sync(0xffffffffu, s0, 0);
+                    want = __shfl_sync(0xffffffffu, want, 0);
+                    const int ipl = want >> 5;
                     more = s0 < total_slots;
                     if (more && lane == 0) {   // entries whose first slot falls into this step
-                        const int s1 = s0 + step_slots < total_slots ? s0 + step_slots : total_slots;
+                        const int s1 = s0 + want < total_slots ? s0 + want : total_slots;
                         n_exp += ((s1 + a.deg_pad - 1) >> a.deg_shift) - ((s0 + a.deg_pad - 1) >> a.deg_shift);
                     }
 #pragma unroll
