@@ -43,7 +43,7 @@ bool dir_exists(const std::string& p) {
 // Exact k nearest among the rows that are alive: a wider exact list from the library, deleted ids
 // dropped on the host.
 std::vector<int> live_ground_truth(IndexGPU& index, const float* queries, int nq, int k, const std::vector<char>& dead) {
-    const int wide = std::min<int>(256, (int)index.size());
+    const int wide = std::min<int>(228, (int)index.size());   // the exact search's widest list
     std::vector<int32_t> ids((size_t)nq * wide);
     int64_t uncertified = 0;
     const int rc = coral_exact_knn(index.handle(), queries, nq, wide, ids.data(), nullptr, &uncertified);
@@ -55,7 +55,7 @@ std::vector<int> live_ground_truth(IndexGPU& index, const float* queries, int nq
             const int id = ids[(size_t)q * wide + j];
             if (id >= 0 && !dead[(size_t)id]) gt[(size_t)q * k + w++] = id;
         }
-        if (w < k) throw std::runtime_error("ground truth: fewer than k live points among the 256 nearest");
+        if (w < k) throw std::runtime_error("ground truth: fewer than k live points among the 228 nearest");
     }
     return gt;
 }

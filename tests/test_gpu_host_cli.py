@@ -327,3 +327,34 @@ def test_build_driver_writes_the_graph_the_library_builds(tmp_path, from_lists):
     st = np.empty(64, np.int32)
     m = host.coral_host_start_ids_load(str(tmp_path / "graph" / "graph.search_start_ids").encode(), st.ctypes.data, 64)
     assert m == len(want_starts) and np.array_equal(st[:m], want_starts)
+
+
+@pytest.mark.parametrize("metric", ["l2", "ip"])
+def test_ground_truth_tool_matches_the_brute_force_oracle(tmp_path, metric):
+    """comp_gt with the reference's flags (tests/comp_gt.cpp): exact lists in the ground-truth file
+    format, equal to the CPU brute force (same distance arithmetic, ties by id)."""
+    build_host.build()
+    rng = np.random.default_rng(3)
+    base = rng.standard_normal((7000, 72), dtype=np.float32)
+    q = rng.standard_normal((130, 72), dtype=np.float32)
+    for name, arr in (("base", base), ("query", q)):
+        (tmp_path / f"{name}.fbin").write_bytes(struct.pack("<ii", *arr.shape) + arr.tobytes())
+    exe = os.path.join(os.path.dirname(build_host.HOST_LIB), "comp_gt")
+    r = subprocess.run([exe, "--data_type", "float", "--dist", metric, "--base_data_path", str(tmp_path / "base.fbin"),
+                        "--query_data_path", str(tmp_path / "query.fbin"), "--gt_save_file", str(tmp_path / "gt.bin"),
+                        "--k", "20", "--nq", "100"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    raw = (tmp_path / "gt.bin").read_bytes()
+    nq, k = struct.unpack("<ii", raw[:8])
+    assert (nq, k) == (100, 20)
+    got = np.frombuffer(raw[8:], dtype=np.int32).reshape(nq, k)
+    if metric == "ip":
+        import ctypes as C
+        host = C.CDLL(build_host.HOST_LIB)
+        host.coral_host_fbin_load.argtypes = [C.c_char_p, C.c_void_p, C.c_int64, C.POINTER(C.c_int64), C.POINTER(C.c_int), C.c_int]
+        for name, arr in (("base", base), ("query", q)):
+            nn, dd = C.c_int64(0), C.c_int(0)
+            assert host.coral_host_fbin_load(str(tmp_path / f"{name}.fbin").encode(), arr.ctypes.data, arr.size, C.byref(nn),
+                                             C.byref(dd), 1) == 0
+    want, _ = oracle.exact_knn(base, q[:100], 20, metric)
+    assert np.array_equal(got, want)
