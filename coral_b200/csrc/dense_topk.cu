@@ -311,6 +311,16 @@ dense_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // in the epilogue: a warp that gives up on a wait must not leave the others waiting for it)
         float* snorm = reinterpret_cast<float*>(smem + kOffNorm) + (size_t)(warp - 2) * kDenseTileN;
         bool ok = true;
+        // keep == 8 (the scheduling keys: few columns, a handful of survivors): the thread also tracks
+        // the eight best scores of its row in registers and filters against the eighth, so the
+        // threshold tightens with every accepted column instead of once per compaction -- about
+        // 8 ln(columns / 8) keys reach the buffer and no compaction runs before the last one.  The
+        // list starts as eight copies of the row's threshold, a lower bound of the keys already kept,
+        // so the eighth entry never exceeds the true eighth best.
+        const bool track8 = a.keep == 8;
+        float top[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) top[i] = thr;
         for (int t = t0; t < t1 && ok; ++t) {
             const int b = (t - t0) & 1;
             const int col0 = t * kDenseTileN;
@@ -326,6 +336,8 @@ dense_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 if (lane == src) {
                     cnt = kept;
                     thr = new_thr;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) top[i] = fmaxf(top[i], new_thr);
                 }
             }
             if (a.metric == 0) {
@@ -351,7 +363,19 @@ dense_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     for (int j = 0; j < 32; ++j) {
                         float s = __uint_as_float(r[j]);
                         if (a.metric == 0) s = fmaf(2.f, s, -snorm[c + j]);
-                        if (s >= thr && c + j < valid) my_keys[cnt++] = score_key(s, a.col_base + (uint32_t)(col0 + c + j));
+                        if (s >= thr && c + j < valid) {
+                            my_keys[cnt++] = score_key(s, a.col_base + (uint32_t)(col0 + c + j));
+                            if (track8) {   // insert s into the descending list, drop its last entry
+                                float v = s;
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    const float hi = fmaxf(top[i], v);
+                                    v = fminf(top[i], v);
+                                    top[i] = hi;
+                                }
+                                thr = top[7];
+                            }
+                        }
                     }
                 }
             }
