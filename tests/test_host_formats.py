@@ -190,3 +190,17 @@ def test_config_json_flat_object(host, tmp_path):
     assert host.coral_host_config_get(str(p).encode(), b"absent", C.byref(v)) == 1
     p.write_text('{"dim": }')
     assert host.coral_host_config_get(str(p).encode(), b"dim", C.byref(v)) == -1
+
+
+@pytest.mark.parametrize("tool,flag", [("test_search_pipeline", "data_type"), ("test_build_pipeline", "data_type"),
+                                       ("test_update", "dataset"), ("comp_gt", "base_data_path")])
+def test_drivers_name_a_missing_required_flag(tool, flag):
+    """Every driver parses the reference's flags by hand: without its required ones it names the first
+    that is missing and returns the reference's -1 before touching a GPU; --help exits 0."""
+    import subprocess
+    build_host.build()
+    exe = os.path.join(os.path.dirname(build_host.HOST_LIB), tool)
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 255 and f"--{flag}' is required" in r.stderr
+    r = subprocess.run([exe, "--help"], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and "flags" in r.stdout
