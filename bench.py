@@ -549,6 +549,10 @@ def main():
     device = f"cuda:{local}"
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # The only collectives here are barriers, scalar reductions and one all-gather of a few MB per
+        # step in the sharded workloads: in-switch reduction buys nothing, and every figure of this
+        # repository was measured with plain peer transport.  An explicit setting wins.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         # NCCL writes its version banner to stdout at NCCL_DEBUG=VERSION; stdout is for the one JSON line
         if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"
