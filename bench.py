@@ -68,7 +68,7 @@ PEAK_FALLBACK_GBS = 6650.0
 # summarised under profiles/ (a profile constant, not a measurement of this run): workload -> ratio.
 # The 10M x 512 workloads use the same ratio: with a 23 GB index L2 serves less of the gather than
 # with 2.3 GB, so for them the figure is a lower bound of the DRAM share.
-DRAM_PER_ALGORITHMIC_BYTE = {"small": 0.743, "c3": 0.743}
+DRAM_PER_ALGORITHMIC_BYTE = {"small": 0.748, "c3": 0.748}
 
 
 _RESULT_FD = None
@@ -772,7 +772,7 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_kind,
                          "traffic": (ratio * alg_bytes if ratio and world == 1 else None),
-                         "traffic_source": (("profile constant: 0.743 DRAM bytes per algorithmic byte in the ncu capture of the "
+                         "traffic_source": (("profile constant: 0.748 DRAM bytes per algorithmic byte in the ncu capture of the "
                                              "1M x 512 case (profiles/), scaled to this launch by its algorithmic bytes"
                                              + ("; a lower bound at 10M, where L2 serves less" if w["n"] > 1_000_000 else ""))
                                             if ratio else None),
