@@ -316,6 +316,9 @@ __global__ void gather_rows_kernel(const float* __restrict__ vecs, const int32_t
     }
 }
 
+constexpr int kCeRowFloats = 68;                          // 64 floats of a row chunk + 4 of padding (bank spread)
+constexpr int kCeStageBytes = 32 * kCeRowFloats * 4;      // one chunk of 32 rows per warp
+
 // Reverse edges (src/enhance.cu:136-212): one warp per (isolated node, result rank) pair that won
 // the found node.  The lanes evaluate, for every position of the found node's row, the three
 // comparisons the reference's loops make (each needs the distance between the isolated node and the
@@ -343,41 +346,119 @@ __global__ void __launch_bounds__(128) ce_reverse_kernel(const float* __restrict
     int32_t* nb = adj + (size_t)knn_id * deg_pad;
     float* ds = ndist + (size_t)knn_id * deg_pad;
     const int d = deg[knn_id];
-    for (int o = lane; o < d; o += 32) {
-        const float dso = ds[o];
-        const float dio = dist_seq(iso_vec, vecs + (size_t)nb[o] * dim, dim, metric);
-        uint8_t f = 0;
-        if (closer(knn_dist, dso, metric)) f |= 1;
-        if (closer(knn_dist, dio, metric)) f |= 2;
-        if (closer(dso, dio, metric)) f |= 4;
-        flags[warp][o] = f;
+    // Distances from the isolated node to the stored neighbours: lane o owns neighbour o's chain
+    // (same order as dist_seq), but the rows are staged through shared memory 64 floats at a time
+    // by the whole warp (two rows per load instruction, whole lines), instead of every lane walking
+    // its own row through L1 sixteen bytes at a time.
+    extern __shared__ __align__(16) unsigned char ce_smem[];
+    float* s_iso = reinterpret_cast<float*>(ce_smem + (size_t)warp * ((size_t)dim * 4 + kCeStageBytes));
+    float* s_rows = s_iso + dim;
+    for (int v = lane; v < dim / 4; v += 32)
+        reinterpret_cast<float4*>(s_iso)[v] = __ldg(reinterpret_cast<const float4*>(iso_vec) + v);
+    for (int o0 = 0; o0 < d; o0 += 32) {
+        const int rows = d - o0 < 32 ? d - o0 : 32;
+        const int o = o0 + lane;
+        float acc = 0.f;
+        for (int c0 = 0; c0 < dim; c0 += 64) {
+            const int units = (dim - c0 < 64 ? dim - c0 : 64) / 4;       // float4 units of this chunk
+            __syncwarp();
+            // all of the chunk's loads are in flight before the first one is stored (a 32-row chunk is 16
+            // loads per lane: two rows per warp-wide load)
+            float4 tmp[16];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                const int r = 2 * k + (lane >> 4), u = lane & 15;
+                if (r < rows && u < units)
+                    tmp[k] = __ldg(reinterpret_cast<const float4*>(vecs + (size_t)nb[o0 + r] * dim + c0) + u);
+            }
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                const int r = 2 * k + (lane >> 4), u = lane & 15;
+                if (r < rows && u < units) *reinterpret_cast<float4*>(s_rows + r * kCeRowFloats + u * 4) = tmp[k];
+            }
+            __syncwarp();
+            if (lane < rows) {
+                const float4* y = reinterpret_cast<const float4*>(s_rows + lane * kCeRowFloats);
+                const float4* x = reinterpret_cast<const float4*>(s_iso + c0);
+                for (int u = 0; u < units; ++u) {
+                    const float4 p = x[u], q = y[u];
+                    if (metric == 0) {
+                        float t;
+                        t = p.x - q.x; acc = fmaf(t, t, acc);
+                        t = p.y - q.y; acc = fmaf(t, t, acc);
+                        t = p.z - q.z; acc = fmaf(t, t, acc);
+                        t = p.w - q.w; acc = fmaf(t, t, acc);
+                    } else {
+                        acc = fmaf(p.x, q.x, acc);
+                        acc = fmaf(p.y, q.y, acc);
+                        acc = fmaf(p.z, q.z, acc);
+                        acc = fmaf(p.w, q.w, acc);
+                    }
+                }
+            }
+        }
+        if (lane < rows) {
+            const float dso = ds[o], dio = acc;
+            uint8_t f = 0;
+            if (closer(knn_dist, dso, metric)) f |= 1;
+            if (closer(knn_dist, dio, metric)) f |= 2;
+            if (closer(dso, dio, metric)) f |= 4;
+            flags[warp][o] = f;
+        }
     }
     __syncwarp();
-    if (lane != 0) return;
-    const uint8_t* F = flags[warp];
-    int pos = 0, valid = 1, out_pos;
-    for (; pos < d; ++pos) {                                   // :172-181
-        if (F[pos] & 1) {
-            if (valid && (F[pos] & 2)) valid = 0;
-        } else
-            break;
+    // lane 0 walks the flags in the reference's order; the warp then shifts the row together
+    int pos = 0, out_pos = -1, insert = 0;
+    if (lane == 0) {
+        const uint8_t* F = flags[warp];
+        int valid = 1;
+        for (; pos < d; ++pos) {                                   // :172-181
+            if (F[pos] & 1) {
+                if (valid && (F[pos] & 2)) valid = 0;
+            } else
+                break;
+        }
+        if (d == max_degree) {                                     // :183-191
+            if (valid && pos < d) {
+                out_pos = d - 1;
+                for (; out_pos >= pos; --out_pos)
+                    if (F[out_pos] & 4) break;
+                if (out_pos < pos) out_pos = d - 1;
+                insert = 1;
+            }
+        } else {
+            out_pos = d;
+            deg[knn_id] = d + 1;
+            insert = 1;
+        }
     }
-    if (d == max_degree) {                                     // :183-191
-        if (!valid || pos >= d) return;
-        out_pos = d - 1;
-        for (; out_pos >= pos; --out_pos)
-            if (F[out_pos] & 4) break;
-        if (out_pos < pos) out_pos = d - 1;
-    } else {
-        out_pos = d;
-        deg[knn_id] = d + 1;
+    insert = __shfl_sync(0xffffffffu, insert, 0);
+    if (!insert) return;
+    pos = __shfl_sync(0xffffffffu, pos, 0);
+    out_pos = __shfl_sync(0xffffffffu, out_pos, 0);
+    // entries pos .. out_pos-1 move one place up, the isolated node takes place pos (:206-211)
+    int32_t vn[4];
+    float vd[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const int j = lane + 32 * t;
+        if (j > pos && j <= out_pos) {
+            vn[t] = nb[j - 1];
+            vd[t] = ds[j - 1];
+        }
     }
-    for (int j = out_pos; j > pos; --j) {                      // :206-211
-        nb[j] = nb[j - 1];
-        ds[j] = ds[j - 1];
+    __syncwarp();
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const int j = lane + 32 * t;
+        if (j > pos && j <= out_pos) {
+            nb[j] = vn[t];
+            ds[j] = vd[t];
+        } else if (j == pos) {
+            nb[j] = iso_id;
+            ds[j] = knn_dist;
+        }
     }
-    nb[pos] = iso_id;
-    ds[pos] = knn_dist;
 }
 
 // Every isolated node's own row from its pruned search results (src/enhance.cu:344-389, :528-580).
@@ -648,7 +729,13 @@ cudaError_t ce_batch(const BuildGraph& g, const int32_t* d_iso_ids, int n_iso, c
     if (kb < 1 || kb > 128 || g.max_degree > 128) return cudaErrorInvalidValue;
     const long long entries = (long long)n_iso * kb;
     claim_kernel<<<grid_for(entries, 256, 2048), 256, 0, st>>>(d_res_ids, entries, g.n, g.claim);
-    ce_reverse_kernel<<<(unsigned)((entries + 3) / 4), 128, 0, st>>>(g.vecs, g.dim, g.metric, g.adj, g.ndist, g.deg, g.deg_pad,
+    const size_t rev_smem = 4 * ((size_t)g.dim * 4 + kCeStageBytes);
+    if (rev_smem > 48 * 1024) {
+        if (rev_smem > 200 * 1024) return cudaErrorInvalidValue;
+        cudaError_t e = cudaFuncSetAttribute(ce_reverse_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rev_smem);
+        if (e != cudaSuccess) return e;
+    }
+    ce_reverse_kernel<<<(unsigned)((entries + 3) / 4), 128, rev_smem, st>>>(g.vecs, g.dim, g.metric, g.adj, g.ndist, g.deg, g.deg_pad,
                                                                      g.max_degree, d_iso_ids, n_iso, d_res_ids, d_res_dists,
                                                                      kb, g.n, g.claim, mode);
     ce_prune_kernel<<<(unsigned)((n_iso + 3) / 4), 128, 0, st>>>(g.vecs, g.dim, g.metric, g.adj, g.ndist, g.deg, g.deg_pad,
